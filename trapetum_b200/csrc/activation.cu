@@ -144,3 +144,35 @@ extern "C" int tb_add_bias(void* x, int x_dtype, long long row_stride, const voi
 #undef LAUNCH
     return tb_launch_status();
 }
+
+// Activation of a feed-forward without a gate branch: out = act(u), act = relu(u)^2 (code 3).  The input is a window of
+// `inter` columns, starting at column col0, of a product given as 32-bit partial sums [splits][rows][row_stride]
+// (added here in split order), so that one product may carry other columns beside it (a router's logits).
+#define ACT_RELU2 3
+
+template <typename TO>
+__global__ void unary_act_kernel(const float* __restrict__ part, int n_splits, long long split_stride, long long row_stride,
+                                 int col0, TO* __restrict__ out, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t row = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= inter) return;
+    const float* p = part + row * row_stride + col0 + c;
+    float u = 0.f;
+    for (int s = 0; s < n_splits; s++) u += p[(size_t)s * split_stride];
+    u = fmaxf(u, 0.f);
+    out[row * inter + c] = from_f<TO>(u * u);
+}
+
+extern "C" int tb_unary_act(const float* part, int n_splits, long long split_stride, long long row_stride, int col0,
+                            void* out, int out_dtype, int rows, int inter, int act, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (inter <= 0 || n_splits < 1 || col0 < 0) return tb_refuse("unary_act: %d columns from column %d of %d partial sums", inter, col0, n_splits);
+    if (act != ACT_RELU2) return tb_refuse("unary_act: unknown activation %d (3: the square of relu)", act);
+    dim3 grid(rows, (inter + 255) / 256);
+    if (grid.y > 65535) return tb_refuse("unary_act: %d columns are too many", inter);
+    TB_DISPATCH_1(out_dtype, T, tb_launch(unary_act_kernel<T>, dim3(grid), dim3(256), 0, stream, part, n_splits, split_stride,
+                                          row_stride, col0, (T*)out, inter));
+    return tb_launch_status();
+}

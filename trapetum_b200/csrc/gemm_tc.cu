@@ -54,6 +54,7 @@ struct GemmParams {
     float scale;                     // the output times this (1 for a plain product); after the cap, never with it
     int act;                         // gated epilogue: 0 gelu_tanh, 1 silu, 2 clamped_swish (only with GATED kernels)
     float limit;                     // clamped_swish: both branches are bounded by it
+    int unary;                       // plain epilogues: 0 nothing, 1 every output becomes relu(v)^2 (never on partial sums)
     // Grouped products (token-major tiles only): tile tp of the tokens multiplies the weight rows of group
     // tile_group[tp], which start at row tile_group[tp] * group_rows of the weight operand; a negative entry: the tile
     // is not in use and nobody touches it.  Null: one group.
@@ -106,6 +107,13 @@ template <int BN, bool SWAP, bool WIDE = false> struct Cfg {
 };
 
 // Epilogue of token-major tiles: the thread holds CH consecutive columns (weight rows q0 .. q0 + CH - 1) of token prow.
+// What a plain epilogue does to one output before the scale: the cap, then the unary activation.
+__device__ __forceinline__ float pointwise(float v, const GemmParams& p) {
+    if (p.cap > 0.f) v = softcap_f(v, p.cap);
+    if (p.unary == 1) { v = fmaxf(v, 0.f); v *= v; }
+    return v;
+}
+
 template <typename TOut, bool GATED, int CH>
 __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, int q0, int sp, const GemmParams& p) {
     static_assert(!GATED || CH == 32, "a gate and its up value lie 16 columns apart");
@@ -146,7 +154,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
                             float v0 = __uint_as_float(r[j + 2 * e]), v1 = __uint_as_float(r[j + 2 * e + 1]);
-                            if (p.cap > 0.f) { v0 = softcap_f(v0, p.cap); v1 = softcap_f(v1, p.cap); }
+                            v0 = pointwise(v0, p); v1 = pointwise(v1, p);
                             v0 *= p.scale; v1 *= p.scale;
                             __nv_bfloat162 h2 = __floats2bfloat162_rn(v0, v1);
                             w[e] = *(uint32_t*)&h2;
@@ -158,8 +166,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
                     for (int j = 0; j < CH; j += 4) {
                         float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
                                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                        if (p.cap > 0.f) { v.x = softcap_f(v.x, p.cap); v.y = softcap_f(v.y, p.cap);
-                                           v.z = softcap_f(v.z, p.cap); v.w = softcap_f(v.w, p.cap); }
+                        v.x = pointwise(v.x, p); v.y = pointwise(v.y, p); v.z = pointwise(v.z, p); v.w = pointwise(v.w, p);
                         v.x *= p.scale; v.y *= p.scale; v.z *= p.scale; v.w *= p.scale;
                         *(float4*)((float*)dst + j) = v;
                     }
@@ -167,7 +174,7 @@ __device__ __forceinline__ void store_token_major(const uint32_t* r, int prow, i
 #pragma unroll
                     for (int j = 0; j < CH; j++) if (q0 + j < p.rows_q) {
                         float v = __uint_as_float(r[j]);
-                        if (p.cap > 0.f) v = softcap_f(v, p.cap);
+                        v = pointwise(v, p);
                         dst[j] = from_f<TOut>(v * p.scale);
                     }
                 }
@@ -355,7 +362,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             if (p.splits > 1) {
                                 p.partial[((size_t)sp * p.rows_q + tok) * p.rows_p + prow] = v;
                             } else {
-                                if (p.cap > 0.f) v = softcap_f(v, p.cap);
+                                v = pointwise(v, p);
                                 ((TOut*)p.out)[(size_t)tok * p.ld_out + prow] = from_f<TOut>(v * p.scale);
                             }
                         }
@@ -696,10 +703,13 @@ extern "C" int tb_gemm_tc_effective_splits(int K, int splits) {
 // reduce = 0 with splits > 1: leave the partial sums in `scratch` ([splits][M][N]) for the consumer to add.
 // out_scale: the output times this number (1: a plain product; not with a cap, not on partial sums that are left).
 // act_limit: the limit of the gated activation 2 (clamped_swish).
-extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
-                             long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
-                             int reduce, int gated_act, float act_limit, float out_scale, cudaStream_t stream) {
+static int gemm_tc_run(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                       long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
+                       int reduce, int gated_act, float act_limit, float out_scale, int unary, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
+    if (unary < 0 || unary > 1) return tb_refuse("gemm_tc: unknown unary activation %d", unary);
+    if (unary && (gated_act >= 0 || softcap > 0.f)) return tb_refuse("gemm_tc: a unary activation goes with neither a gate nor a cap");
+    if (unary) splits = 1;                           // the activation is not linear: no partial sums
     if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
         return tb_refuse("gemm_tc: needs K, lda, ldw multiples of 8 and 16-byte aligned operands "
                          "(M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, lda, ldw);
@@ -738,6 +748,7 @@ extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype,
     p.out = C; p.ld_out = ldc; p.partial = scratch; p.cap = splits > 1 ? 0.f : softcap;
     p.act = gated ? gated_act : 0;
     p.limit = act_limit;
+    p.unary = unary;
     if (out_scale != 1.0f && (softcap > 0.f || gated || (splits > 1 && !reduce)))
         return tb_refuse("gemm_tc: an output scale goes with neither a cap, a gated epilogue nor partial sums");
     p.scale = splits > 1 ? 1.0f : out_scale;
@@ -797,10 +808,11 @@ extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype,
 // tile of 128 belongs to one group.  gated_act >= 0: the gated epilogue on rows interleaved per group (N = 2 x the
 // output's width, bfloat16 out); else a plain product into C (bfloat16 or float32).  tile_group: device memory,
 // [ceil(M / 128)] group numbers in [0, groups), or -1 for a tile that is not in use (its rows of C are not written).
-extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
-                                  long long lda, long long ldw, long long ldc, const int* tile_group, int gated_act,
-                                  cudaStream_t stream) {
+static int gemm_tc_grouped_run(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
+                               long long lda, long long ldw, long long ldc, const int* tile_group, int gated_act,
+                               int unary, cudaStream_t stream) {
     if (M <= 0 || N <= 0 || groups <= 0) return 0;
+    if (unary < 0 || unary > 1 || (unary && gated_act >= 0)) return tb_refuse("gemm_tc_grouped: unary activation %d (with gate %d)", unary, gated_act);
     if (!tb_gemm_tc_takes(A, W, M, N, K, lda, ldw))
         return tb_refuse("gemm_tc_grouped: needs K, lda, ldw multiples of 8 and 16-byte aligned operands");
     if (c_dtype != TB_F32 && c_dtype != TB_BF16) return tb_refuse("gemm_tc_grouped: unknown output dtype %d", c_dtype);
@@ -819,7 +831,7 @@ extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_d
     p.tile_group = tile_group; p.group_rows = N;
     p.K = K; p.kblocks = (K + BK - 1) / BK; p.splits = 1; p.kb_per_split = p.kblocks;
     p.out = C; p.ld_out = ldc; p.partial = nullptr; p.cap = 0.f; p.scale = 1.0f;
-    p.act = gated ? gated_act : 0; p.limit = 0.f;
+    p.act = gated ? gated_act : 0; p.limit = 0.f; p.unary = unary;
     p.rows_p = M; p.rows_q = N;
     CUtensorMap mp, mq;
     if (make_map(&mp, A, M, K, lda, BM) || make_map(&mq, W, groups * N, K, ldw, bn)) return -1;
@@ -828,6 +840,31 @@ extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_d
     if (gated) return bn == 256 ? launch<256, false, bf16, true>(mp, mq, p, stream) : launch<128, false, bf16, true>(mp, mq, p, stream);
     if (c_dtype == TB_BF16) return bn == 256 ? launch<256, false, bf16>(mp, mq, p, stream) : launch<128, false, bf16>(mp, mq, p, stream);
     return bn == 256 ? launch<256, false, float>(mp, mq, p, stream) : launch<128, false, float>(mp, mq, p, stream);
+}
+
+extern "C" int tb_gemm_tc_grouped(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
+                                  long long lda, long long ldw, long long ldc, const int* tile_group, int gated_act,
+                                  cudaStream_t stream) {
+    return gemm_tc_grouped_run(A, W, C, c_dtype, M, N, groups, K, lda, ldw, ldc, tile_group, gated_act, 0, stream);
+}
+
+// The grouped product whose every output becomes relu(v)^2 (unary = 1): experts without a gate branch.
+extern "C" int tb_gemm_tc_grouped_unary(const void* A, const void* W, void* C, int c_dtype, int M, int N, int groups, int K,
+                                        long long lda, long long ldw, long long ldc, const int* tile_group, int unary,
+                                        cudaStream_t stream) {
+    return gemm_tc_grouped_run(A, W, C, c_dtype, M, N, groups, K, lda, ldw, ldc, tile_group, -1, unary, stream);
+}
+
+extern "C" int tb_gemm_tc_ex(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                             long long lda, long long ldw, long long ldc, float softcap, int splits, float* scratch,
+                             int reduce, int gated_act, float act_limit, float out_scale, cudaStream_t stream) {
+    return gemm_tc_run(A, W, C, c_dtype, M, N, K, lda, ldw, ldc, softcap, splits, scratch, reduce, gated_act, act_limit, out_scale, 0, stream);
+}
+
+// The plain product whose every output becomes relu(v)^2 (unary = 1): a feed-forward without a gate branch.
+extern "C" int tb_gemm_tc_unary(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,
+                                long long lda, long long ldw, long long ldc, int unary, cudaStream_t stream) {
+    return gemm_tc_run(A, W, C, c_dtype, M, N, K, lda, ldw, ldc, 0.f, 1, nullptr, 0, -1, 0.f, 1.0f, unary, stream);
 }
 
 extern "C" int tb_gemm_tc(const void* A, const void* W, void* C, int c_dtype, int M, int N, int K,

@@ -1,13 +1,14 @@
 // A feed-forward made of experts behind a router.
 //
 //   tb_moe_route     per token, from the logits z = R x (32-bit sums of a product, given as split-K partial sums):
-//                    scores s = sigmoid(z); choice scores s + correction;
+//                    scores s = sigmoid(z), or softmax(z) over all experts; choice scores s + correction;
 //                    experts form `groups` equal groups of neighbours, a group's score is the sum of its
 //                    `group_top` largest choice scores, experts outside the `keep` best groups cannot be chosen
 //                    (their choice scores count as minus infinity); the `top` largest choice scores win (the
-//                    lower index on a tie); weights are the winners' s divided by their sum + eps.  Also the
+//                    lower index on a tie); weights are the winners' s divided by their sum + eps, times out_scale.  Also the
 //                    shared expert's gate sigmoid(g . x), one number per token, if asked for.
-//   tb_moe_gate_up   for every (token, chosen expert): act(G_e x) * (U_e x), act = silu
+//   tb_moe_gate_up   for every (token, chosen expert): silu(G_e x) * (U_e x), or, for experts without a gate matrix,
+//                    relu(U_e x)^2
 //   tb_moe_down      out[t] = sum_k weight[t,k] * D_e(t,k) a[t,k]  (+ gate[t] * shared[t], the shared expert's output
 //                    given as 32-bit split-K partial sums), 32-bit
 //
@@ -25,6 +26,8 @@ struct MoeRouteArgs {
     float* gate;                               // [T] (if shared_gate)
     int n_tokens, W, E, top, groups, keep, group_top;
     float weight_eps;
+    int softmax;                               // scores are softmax(z) over the experts instead of sigmoid(z)
+    float out_scale;                           // the weights times this
 };
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -57,10 +60,23 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
         }
         for (; sp < a.splits; sp++) d += src[(size_t)sp * a.split_stride];
         const float s = 1.f / (1.f + expf(-d));
-        if (e < a.E) { score[e] = s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
+        if (e < a.E) { score[e] = a.softmax ? d : s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
         else a.gate[t] = s;
     }
     __syncwarp();
+    if (a.softmax) {
+        float mx = -INFINITY;
+        for (int e = lane; e < a.E; e += 32) mx = fmaxf(mx, score[e]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int e = lane; e < a.E; e += 32) { const float x = expf(score[e] - mx); score[e] = x; sum += x; }
+        sum = warp_sum(sum);
+        for (int e = lane; e < a.E; e += 32) {
+            const float s = score[e] / sum;
+            score[e] = s; choice[e] = s + (a.correction ? a.correction[e] : 0.f);
+        }
+        __syncwarp();
+    }
     if (a.groups > 1) {
         const int per = a.E / a.groups;
         for (int g = lane; g < a.groups; g += 32) {
@@ -109,7 +125,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
         }
     }
     __syncwarp();
-    const float inv = 1.f / (wsum + a.weight_eps);
+    const float inv = a.out_scale / (wsum + a.weight_eps);
     for (int n = lane; n < a.top; n += 32) a.weight[(size_t)t * a.top + n] *= inv;
 }
 
@@ -123,6 +139,7 @@ struct MoeExpertArgs {
     const float* gate;                         // [T] (with shared)
     float* out;                                // [T][W]
     int n_tokens, W, ff, top;
+    int ungated;                               // experts are D relu(U x)^2: there is no gate matrix
 };
 
 // 16 bytes of a weight row per lane and load where the row allows it; MV_ROWS rows (and for gate/up both matrices) are on
@@ -172,13 +189,14 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
     for (int f0 = (blockIdx.y * nwarp + warp) * MV_ROWS; f0 < a.ff; f0 += gridDim.y * nwarp * MV_ROWS) {
         const int nr = min(MV_ROWS, a.ff - f0);
         float g[MV_ROWS], u[MV_ROWS];
-        mv_dot<T>(gw + (size_t)f0 * a.W, a.W, nr, x_s, a.W, lane, g);
+        if (!a.ungated) mv_dot<T>(gw + (size_t)f0 * a.W, a.W, nr, x_s, a.W, lane, g);
         mv_dot<T>(uw + (size_t)f0 * a.W, a.W, nr, x_s, a.W, lane, u);
         if (lane < nr) {
-            float gv = g[0], uv = u[0];
+            float gv = a.ungated ? 0.f : g[0], uv = u[0];
 #pragma unroll
-            for (int r = 1; r < MV_ROWS; r++) if (lane == r) { gv = g[r]; uv = u[r]; }
-            ((T*)a.act)[(size_t)pair * a.ff + f0 + lane] = from_f<T>(gv / (1.f + expf(-gv)) * uv);
+            for (int r = 1; r < MV_ROWS; r++) if (lane == r) { gv = a.ungated ? 0.f : g[r]; uv = u[r]; }
+            const float y = a.ungated ? fmaxf(uv, 0.f) * fmaxf(uv, 0.f) : gv / (1.f + expf(-gv)) * uv;
+            ((T*)a.act)[(size_t)pair * a.ff + f0 + lane] = from_f<T>(y);
         }
     }
 }
@@ -296,13 +314,15 @@ struct MoeGroupedArgs {
     int W, ff, top;
 };
 
-// GATED: rows of x (by pair / top) times [G_e ; U_e] for 64 columns of ff, then silu(g) * u  ->  act[pair]
-// else:  rows of act (by pair) times D_e for 128 columns of W, times the pair's weight          ->  pair_out[pair]
+// MODE 1: rows of x (by pair / top) times [G_e ; U_e] for 64 columns of ff, then silu(g) * u  ->  act[pair]
+// MODE 2: rows of x (by pair / top) times U_e for 128 columns of ff, then relu(u)^2            ->  act[pair]
+// MODE 0: rows of act (by pair) times D_e for 128 columns of W, times the pair's weight        ->  pair_out[pair]
 // A tile is 128 pairs x 128 weight rows, eight warps (4 x 2) of 32 x 64 each, k in blocks of 64 through a three-stage
 // cp.async ring.  GATED lays the weight rows out so that a warp holds a gate column and its up column in one thread:
 // rows 64w .. 64w+31 of the tile are gate rows n0 + 32w .., rows 64w+32 .. 64w+63 the up rows of the same columns.
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(MG_THREADS, 2) moe_grouped_kernel(MoeGroupedArgs a) {
+    constexpr bool GATED = MODE == 1, FROM_X = MODE != 0;
     pdl_launch_dependents();
     extern __shared__ __align__(16) unsigned char mg_ring[];
     __shared__ int row_src[MG_BM];
@@ -311,22 +331,22 @@ __global__ void __launch_bounds__(MG_THREADS, 2) moe_grouped_kernel(MoeGroupedAr
     pdl_wait();
     if (tile >= *a.n_tiles) return;
     const int e = a.tile_expert[tile], row0 = a.tile_row0[tile], rows = a.tile_rows[tile];
-    const int K = GATED ? a.W : a.ff;
-    const int N = GATED ? a.ff : a.W;
+    const int K = FROM_X ? a.W : a.ff;
+    const int N = FROM_X ? a.ff : a.W;
     const int n0 = blockIdx.y * (GATED ? MG_BN / 2 : MG_BN);
     if (threadIdx.x < MG_BM) row_src[threadIdx.x] = threadIdx.x < rows ? a.perm[row0 + threadIdx.x] : -1;
     __syncthreads();
-    const bf16* A = GATED ? a.x : a.act;
-    const long long a_stride = GATED ? a.x_stride : a.ff;
-    const bf16* B0 = GATED ? a.gate_w + (size_t)e * a.ff * a.W : a.down_w + (size_t)e * a.W * a.ff;
+    const bf16* A = FROM_X ? a.x : a.act;
+    const long long a_stride = FROM_X ? a.x_stride : a.ff;
     const bf16* B1 = a.up_w + (size_t)e * a.ff * a.W;
+    const bf16* B0 = MODE == 1 ? a.gate_w + (size_t)e * a.ff * a.W : (MODE == 2 ? B1 : a.down_w + (size_t)e * a.W * a.ff);
     auto load = [&](int s, int k0) {
         unsigned char* sa = mg_ring + (size_t)s * MG_STAGE_BYTES; unsigned char* sb = sa + MG_BM * MG_PITCH;
         for (int c = threadIdx.x; c < MG_BM * (MG_BK / 8); c += MG_THREADS) {
             const int r = c >> 3, ch = c & 7, k = k0 + ch * 8;
             const int p = row_src[r];
             const bool ok = p >= 0 && k < K;
-            const bf16* src = A + (size_t)(ok ? (GATED ? p / a.top : p) : 0) * a_stride + (ok ? k : 0);
+            const bf16* src = A + (size_t)(ok ? (FROM_X ? p / a.top : p) : 0) * a_stride + (ok ? k : 0);
             mg_cp16(sa + r * MG_PITCH + ch * 16, src, ok);
         }
         for (int c = threadIdx.x; c < MG_BN * (MG_BK / 8); c += MG_THREADS) {
@@ -386,6 +406,18 @@ __global__ void __launch_bounds__(MG_THREADS, 2) moe_grouped_kernel(MoeGroupedAr
                     const float ga = acc[m][n][j], ua = acc[m][n + 4][j], gb = acc[m][n][2 + j], ub = acc[m][n + 4][2 + j];
                     if (pa >= 0) a.act[(size_t)pa * a.ff + col] = __float2bfloat16_rn(ga / (1.f + expf(-ga)) * ua);
                     if (pb >= 0) a.act[(size_t)pb * a.ff + col] = __float2bfloat16_rn(gb / (1.f + expf(-gb)) * ub);
+                }
+            }
+        } else if (MODE == 2) {
+#pragma unroll
+            for (int n = 0; n < 8; n++) {
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const int col = n0 + wn * 64 + n * 8 + cq + j;
+                    if (col >= N) continue;
+                    const float ua = fmaxf(acc[m][n][j], 0.f), ub = fmaxf(acc[m][n][2 + j], 0.f);
+                    if (pa >= 0) a.act[(size_t)pa * a.ff + col] = __float2bfloat16_rn(ua * ua);
+                    if (pb >= 0) a.act[(size_t)pb * a.ff + col] = __float2bfloat16_rn(ub * ub);
                 }
             }
         } else {
@@ -535,15 +567,17 @@ extern "C" int tb_moe_grouped(const MoeGroupedArgs* args, const float* shared, i
     constexpr int SMEM = MG_STAGES * MG_STAGE_BYTES;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e1 != cudaSuccess || e2 != cudaSuccess) return (int)(e1 != cudaSuccess ? e1 : e2);
+        cudaError_t e1 = cudaFuncSetAttribute(moe_grouped_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e2 = cudaFuncSetAttribute(moe_grouped_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        cudaError_t e3 = cudaFuncSetAttribute(moe_grouped_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e1 != cudaSuccess || e2 != cudaSuccess || e3 != cudaSuccess) return (int)(e1 != cudaSuccess ? e1 : (e2 != cudaSuccess ? e2 : e3));
         attr_set = true;
     }
-    tb_launch(moe_grouped_kernel<true>, dim3(max_tiles, (a.ff + 63) / 64), dim3(MG_THREADS), SMEM, stream, a);
+    if (a.gate_w != nullptr) tb_launch(moe_grouped_kernel<1>, dim3(max_tiles, (a.ff + 63) / 64), dim3(MG_THREADS), SMEM, stream, a);
+    else tb_launch(moe_grouped_kernel<2>, dim3(max_tiles, (a.ff + MG_BN - 1) / MG_BN), dim3(MG_THREADS), SMEM, stream, a);   // experts without a gate matrix
     int st = tb_launch_status();
     if (st) return st;
-    tb_launch(moe_grouped_kernel<false>, dim3(max_tiles, (a.W + MG_BN - 1) / MG_BN), dim3(MG_THREADS), SMEM, stream, a);
+    tb_launch(moe_grouped_kernel<0>, dim3(max_tiles, (a.W + MG_BN - 1) / MG_BN), dim3(MG_THREADS), SMEM, stream, a);
     st = tb_launch_status();
     if (st) return st;
     const long long n = (long long)n_tokens * a.W;

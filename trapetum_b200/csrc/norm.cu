@@ -552,6 +552,79 @@ extern "C" int tb_fold_rmsnorm(float* h, int post, float alpha, const void* a, i
     return tb_launch_status();
 }
 
+// Several branches added at once, scaled, and the next norm of the stream in the same pass (arrangements whose
+// sublayers all read one normed input and whose outputs are added together):
+//
+//   h <- h + scale * (a + b)          a, b: 32-bit, each [rows][width] or split-K partial sums; b may be null
+//   then, if asked:  out = h * rsqrt(mean(h^2) + eps) * (offset + w)
+//
+// One CTA per row, the new row kept in shared memory between the two passes when it fits.  Everything is 32-bit.
+template <typename TW, typename TO, int VEC>
+__global__ void add_scaled_rmsnorm_kernel(float* __restrict__ h, float scale, const float* __restrict__ a, int a_splits,
+                                          long long a_stride, const float* __restrict__ b, int b_splits, long long b_stride,
+                                          const TW* __restrict__ w, float eps, float offset, TO* __restrict__ out, int width,
+                                          int row_cache) {
+    pdl_launch_dependents();
+    pdl_wait();
+    extern __shared__ __align__(16) float row[];
+    __shared__ float red[33];
+    const size_t base = (size_t)blockIdx.x * width;
+    const int step = blockDim.x * VEC;
+    float ss = 0.f;
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float v[VEC], u[VEC], hv[VEC];
+        load_sum<float, VEC>(a + base + i, a_splits, a_stride, v);
+        if (b != nullptr) {
+            load_sum<float, VEC>(b + base + i, b_splits, b_stride, u);
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] += u[e];
+        }
+        if (VEC == 4) Vec4<float>::load(h + base + i, hv); else hv[0] = h[base + i];
+#pragma unroll
+        for (int e = 0; e < VEC; e++) { v[e] = fmaf(scale, v[e], hv[e]); ss += v[e] * v[e]; if (row_cache) row[i + e] = v[e]; }
+        if (VEC == 4) Vec4<float>::store(h + base + i, v); else h[base + i] = v[0];
+    }
+    if (out == nullptr) return;
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x * VEC; i < width; i += step) {
+        float v[VEC], g[VEC];
+        if (row_cache) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) v[e] = row[i + e];
+        } else {
+            if (VEC == 4) Vec4<float>::load(h + base + i, v); else v[0] = h[base + i];      // written by this thread
+        }
+        if (VEC == 4) Vec4<TW>::load(w + i, g); else g[0] = to_f<TW>(w[i]);
+#pragma unroll
+        for (int e = 0; e < VEC; e++) v[e] = v[e] * r * (offset + g[e]);
+        if (VEC == 4) Vec4<TO>::store(out + base + i, v); else out[base + i] = from_f<TO>(v[0]);
+    }
+}
+
+// b may be null (one branch); w and out may be null (the sum alone).
+extern "C" int tb_add_scaled_rmsnorm(float* h, float scale, const float* a, int a_splits, long long a_stride,
+                                     const float* b, int b_splits, long long b_stride, const void* w, int w_dtype,
+                                     float eps, float offset, void* out, int out_dtype, int rows, int width,
+                                     cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return tb_refuse("add_scaled_rmsnorm: width=%d", width);
+    if (!code_ok(w_dtype) || !code_ok(out_dtype)) return tb_refuse("add_scaled_rmsnorm: unknown dtype codes %d %d", w_dtype, out_dtype);
+    if (a == nullptr || a_splits < 1 || (b != nullptr && b_splits < 1)) return tb_refuse("add_scaled_rmsnorm: needs a branch");
+    if ((out != nullptr) != (w != nullptr)) return tb_refuse("add_scaled_rmsnorm: a norm needs its weight and its output");
+    const int row_cache = (size_t)width * sizeof(float) <= 40 * 1024;
+    const size_t smem = row_cache ? (size_t)width * sizeof(float) : 0;
+    const bool vec = width % 4 == 0 && a_stride % 4 == 0 && b_stride % 4 == 0 && aligned16(h) && aligned16(a) && aligned16(b) &&
+                     aligned16(w) && aligned16(out);
+#define ADDS(VEC_)                                                                                                  \
+        DISPATCH3(TB_F32, w_dtype, out_dtype,                                                                       \
+            tb_launch(add_scaled_rmsnorm_kernel<TW, TO, VEC_>, dim3(rows), dim3(norm_threads(width, VEC_)), smem, stream, \
+                h, scale, a, a_splits, a_stride, b, b_splits, b_stride, (const TW*)w, eps, offset, (TO*)out, width, row_cache))
+    if (vec) ADDS(4); else ADDS(1);
+#undef ADDS
+    return tb_launch_status();
+}
+
 // out = x rounded to the compute dtype (a 32-bit stream read by a 16-bit product).
 template <typename TO>
 __global__ void cast_kernel(const float* __restrict__ x, TO* __restrict__ out, size_t n) {

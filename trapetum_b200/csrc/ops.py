@@ -212,6 +212,43 @@ def fold_rmsnorm(h: torch.Tensor, a: torch.Tensor, w: torch.Tensor, eps: float, 
     return out
 
 
+def _branch(h: torch.Tensor, a: torch.Tensor, what: str):
+    """(pointer, splits, split stride) of a float32 branch output [rows, width] or [splits, rows, width]."""
+    if a.dtype != torch.float32:
+        raise KernelError(f"{what}: branch outputs must be float32, got {a.dtype}")
+    if a.dim() == 3:
+        if tuple(a.shape[1:]) != tuple(h.shape) or a.stride(1) != h.shape[1] or a.stride(2) != 1:
+            raise KernelError(f"{what}: partial sums {tuple(a.shape)} do not fit the stream {tuple(h.shape)}")
+        return a, a.shape[0], a.stride(0)
+    if a.shape != h.shape or not a.is_contiguous():
+        raise KernelError(f"{what}: branch {tuple(a.shape)} does not fit the stream {tuple(h.shape)}")
+    return a, 1, 0
+
+
+def add_scaled_rmsnorm(h: torch.Tensor, branches, scale: float, w: Optional[torch.Tensor] = None, eps: float = 0.0,
+                       offset: float = 0.0, out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """``h += scale * (sum of the branches)`` in place (h float32; one or two float32 branch outputs, each [rows, width]
+    or [splits, rows, width] partial sums); with ``w`` also returns ``norm(h) * (offset + w)`` in ``out_dtype``."""
+    _cuda(h, w, *branches)
+    if h.dtype != torch.float32 or h.dim() != 2 or not h.is_contiguous():
+        raise KernelError("add_scaled_rmsnorm: the residual stream must be contiguous float32 [rows, width]")
+    if not 1 <= len(branches) <= 2:
+        raise KernelError(f"add_scaled_rmsnorm: one or two branches, got {len(branches)}")
+    a, a_n, a_s = _branch(h, branches[0], "add_scaled_rmsnorm")
+    b, b_n, b_s = _branch(h, branches[1], "add_scaled_rmsnorm") if len(branches) == 2 else (None, 0, 0)
+    out = None
+    if w is not None:
+        if w.numel() != h.shape[1] or not w.is_contiguous():
+            raise KernelError("add_scaled_rmsnorm: the norm weight does not fit the row width")
+        out = torch.empty(h.shape, dtype=out_dtype, device=h.device)
+    lib = build.load("norm")
+    _check(lib, lib.tb_add_scaled_rmsnorm(_ptr(h), c_float(scale), _ptr(a), c_int(a_n), c_longlong(a_s), _ptr(b), c_int(b_n),
+                                          c_longlong(b_s), _ptr(w), c_int(code(w.dtype) if w is not None else 0), c_float(eps),
+                                          c_float(offset), _ptr(out), c_int(code(out_dtype) if out is not None else 0),
+                                          c_int(h.shape[0]), c_int(h.shape[1]), _stream()), "add_scaled_rmsnorm")
+    return out
+
+
 def cast(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
     """A float32 tensor rounded to ``out_dtype``."""
     _cuda(x)
@@ -225,6 +262,7 @@ def cast(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
 
 # ---------------------------------------------------------------------------
 ACTIVATIONS = {"gelu_tanh": 0, "silu": 1, "clamped_swish": 2}
+UNARY_ACTIVATIONS = {"relu2": 3}          # activations of a feed-forward without a gate branch: relu2(u) = relu(u)^2
 ACTIVATIONS_WITH_LIMIT = ("clamped_swish",)
 
 
@@ -242,6 +280,28 @@ def gated_act(gu: torch.Tensor, activation: str, out_dtype: torch.dtype, limit: 
     _check(lib, lib.tb_gated_act_limit(_ptr(gu), c_int(code(gu.dtype)), _ptr(out), c_int(code(out_dtype)),
                                        c_int(gu.shape[0]), c_int(inter), c_int(ACTIVATIONS[activation]),
                                        c_float(limit), _stream()), "gated_act")
+    return out
+
+
+def unary_act(part: torch.Tensor, activation: str, out_dtype: torch.dtype, col0: int = 0,
+              cols: Optional[int] = None) -> torch.Tensor:
+    """``act`` of columns ``col0 .. col0 + cols`` of a product given as float32 [rows, width] or partial sums
+    [splits, rows, width] (added in split order); returns [rows, cols] in ``out_dtype``."""
+    _cuda(part)
+    if part.dim() == 2:
+        part = part[None]
+    if part.dtype != torch.float32 or part.dim() != 3 or part.stride(2) != 1:
+        raise KernelError("unary_act: wants float32 [splits, rows, width] with contiguous rows")
+    if activation not in UNARY_ACTIVATIONS:
+        raise KernelError(f"unary_act: unknown activation '{activation}' (known: {sorted(UNARY_ACTIVATIONS)})")
+    cols = part.shape[2] - col0 if cols is None else cols
+    if col0 < 0 or cols < 1 or col0 + cols > part.shape[2]:
+        raise KernelError(f"unary_act: columns {col0}..{col0 + cols} lie outside a width of {part.shape[2]}")
+    out = torch.empty((part.shape[1], cols), dtype=out_dtype, device=part.device)
+    lib = build.load("activation")
+    _check(lib, lib.tb_unary_act(_ptr(part), c_int(part.shape[0]), c_longlong(part.stride(0)), c_longlong(part.stride(1)),
+                                 c_int(col0), _ptr(out), c_int(code(out_dtype)), c_int(part.shape[1]), c_int(cols),
+                                 c_int(UNARY_ACTIVATIONS[activation]), _stream()), "unary_act")
     return out
 
 
@@ -417,6 +477,86 @@ def headnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: 
     lib = build.load("headnorm_kv")
     _check(lib, lib.tb_headnorm_kv(ctypes.byref(a), c_int(code(out_dtype)), c_int(T), _stream()), "headnorm_kv")
     return out
+
+
+class _ProjNormKvArgs(ctypes.Structure):
+    _fields_ = [("partial", c_void_p), ("n_splits", c_int), ("split_stride", c_longlong), ("partial_row_stride", c_longlong),
+                ("out", c_void_p), ("out_row_stride", c_longlong), ("gate_out", c_void_p),
+                ("n_heads", c_int), ("n_kv_heads", c_int), ("dim", c_int), ("vdim", c_int), ("D", c_int),
+                ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("eps", c_float), ("head_scale", c_void_p),
+                ("rotary_dim", c_int), ("inv_freq", c_void_p),
+                ("positions", c_void_p), ("token_seq", c_void_p), ("len_after", c_void_p),
+                ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("ring_rows", c_int)]
+
+
+def projnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int, padded: int,
+                out_dtype: torch.dtype, q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                head_scale: Optional[torch.Tensor], rotary_dim: int, inv_freq: Optional[torch.Tensor], has_gate: bool,
+                positions: torch.Tensor, token_seq: torch.Tensor, len_after: torch.Tensor,
+                k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
+                ring_rows: int):
+    """From the q/k/v(/gate) product's float32 partial sums [splits, T, H dim + G dim + G vdim (+ H)] to
+    ([T, (H + 2 G) * padded] in ``out_dtype``, sigmoid of the gate columns float32 [T, H] or None): q and k divided by
+    their root mean square over the whole projection times ``q_norm_w`` / ``k_norm_w`` (float32; None: no norm), q heads
+    times ``head_scale[h]`` (float32 [H] or None), the first ``rotary_dim`` dims of every q and k head rotated at the
+    token's position, every head padded with zeros to ``padded`` numbers; k and v are also written to the cache line
+    (pools [pages, G, PAGE_ROWS, padded])."""
+    _cuda(partial, q_norm_w, k_norm_w, head_scale, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table)
+    H, G = n_heads, n_kv_heads
+    in_width = H * dim + G * (dim + vdim) + (H if has_gate else 0)
+    if partial.dtype != torch.float32 or partial.dim() != 3 or partial.stride(2) != 1 or partial.shape[2] < in_width:
+        raise KernelError(f"projnorm_kv: wants float32 partial sums [splits, tokens, >= {in_width}], got {tuple(partial.shape)} {partial.dtype}")
+    T = partial.shape[1]
+    for name, t in (("positions", positions), ("token_seq", token_seq)):
+        if t.dtype != torch.int32 or t.numel() != T or not t.is_contiguous():
+            raise KernelError(f"projnorm_kv: {name} must be contiguous int32 [{T}]")
+    for name, t, n in (("q_norm_w", q_norm_w, H * dim), ("k_norm_w", k_norm_w, G * dim), ("head_scale", head_scale, H),
+                       ("inv_freq", inv_freq, rotary_dim // 2)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelError(f"projnorm_kv: {name} must be contiguous float32 [{n}]")
+    if rotary_dim and inv_freq is None:
+        raise KernelError("projnorm_kv: a rotation needs its table")
+    if k_pool is not None:
+        for p in (k_pool, v_pool):
+            if p is None or p.dtype != out_dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (G, PAGE_ROWS, padded):
+                raise KernelError(f"projnorm_kv: cache pools must be contiguous [pages, {G}, PAGE_ROWS, {padded}] of the output's dtype")
+        if page_table is None or page_table.dtype != torch.int32 or page_table.dim() != 2 or page_table.stride(1) != 1:
+            raise KernelError("projnorm_kv: page_table must be int32 [batch, pages]")
+    out = torch.empty((T, (H + 2 * G) * padded), dtype=out_dtype, device=partial.device)
+    gate = torch.empty((T, H), dtype=torch.float32, device=partial.device) if has_gate else None
+    a = _ProjNormKvArgs()
+    a.partial = partial.data_ptr(); a.n_splits = partial.shape[0]; a.split_stride = partial.stride(0)
+    a.partial_row_stride = partial.stride(1)
+    a.out = out.data_ptr(); a.out_row_stride = out.stride(0); a.gate_out = gate.data_ptr() if gate is not None else None
+    a.n_heads = H; a.n_kv_heads = G; a.dim = dim; a.vdim = vdim; a.D = padded
+    a.q_norm_w = q_norm_w.data_ptr() if q_norm_w is not None else None
+    a.k_norm_w = k_norm_w.data_ptr() if k_norm_w is not None else None
+    a.eps = eps
+    a.head_scale = head_scale.data_ptr() if head_scale is not None else None
+    a.rotary_dim = rotary_dim; a.inv_freq = inv_freq.data_ptr() if (inv_freq is not None and rotary_dim) else None
+    a.positions = positions.data_ptr(); a.token_seq = token_seq.data_ptr(); a.len_after = len_after.data_ptr()
+    a.k_pool = k_pool.data_ptr() if k_pool is not None else None
+    a.v_pool = v_pool.data_ptr() if k_pool is not None else None
+    a.page_table = page_table.data_ptr() if k_pool is not None else None
+    a.pt_stride = page_table.stride(0) if k_pool is not None else 0
+    a.page_rows = PAGE_ROWS; a.ring_rows = ring_rows
+    lib = build.load("projnorm_kv")
+    _check(lib, lib.tb_projnorm_kv(ctypes.byref(a), c_int(code(out_dtype)), c_int(T), _stream()), "projnorm_kv")
+    return out, gate
+
+
+def head_gate(o: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor:
+    """Every head of an attention output ``o`` [T, n_heads * D] times its token's gate [T, n_heads] (float32), in place."""
+    _cuda(o, gate)
+    T = o.shape[0]
+    if o.dim() != 2 or not o.is_contiguous() or o.shape[1] % n_heads or gate.dtype != torch.float32 \
+            or tuple(gate.shape) != (T, n_heads) or not gate.is_contiguous():
+        raise KernelError(f"head_gate: output {tuple(o.shape)} and gate {tuple(gate.shape)} do not fit {n_heads} heads")
+    lib = build.load("projnorm_kv")
+    _check(lib, lib.tb_head_gate(_ptr(o), c_int(code(o.dtype)), _ptr(gate), c_int(T), c_int(n_heads),
+                                 c_int(o.shape[1] // n_heads), _stream()), "head_gate")
+    return o
 
 
 class _Mamba2Args(ctypes.Structure):
@@ -656,7 +796,8 @@ def gemm_tc_gates(activation: str) -> bool:
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: float = 0.0,
             splits: Optional[int] = None, out: Optional[torch.Tensor] = None, partials: bool = False,
-            gated_act: Optional[str] = None, act_limit: float = 0.0, out_scale: float = 1.0) -> torch.Tensor:
+            gated_act: Optional[str] = None, act_limit: float = 0.0, out_scale: float = 1.0,
+            unary_act: Optional[str] = None) -> torch.Tensor:
     """a[M,K] @ w[N,K]^T in bfloat16 on tcgen05 tensor cores with 32-bit accumulation.
     ``splits`` None: the library picks the K split (more than 1 only for few tokens and few weight rows).
     ``partials=True`` returns float32 [splits, M, N] whose sum over the first axis, taken in order, is the
@@ -664,8 +805,18 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, softcap: f
     ``gated_act`` ("gelu_tanh" or "silu"): ``w`` holds gate and up rows interleaved in blocks of 16
     (see :func:`interleave_gate_up`); the result is bfloat16 [M, N/2] = act(gate) * up, taken on the
     32-bit accumulators in the epilogue ("clamped_swish" takes ``act_limit``).  ``out_scale``: the result times this
-    number (not with a cap, a gate or partial sums)."""
+    number (not with a cap, a gate or partial sums).  ``unary_act`` ("relu2"): every output becomes act(output), taken
+    on the 32-bit accumulators (no partial sums, no cap, no gate)."""
     _cuda(a, w, out)
+    if unary_act is not None:
+        if unary_act not in UNARY_ACTIVATIONS or partials or softcap or gated_act is not None or out_scale != 1.0 or not gemm_tc_takes(a, w):
+            raise KernelError(f"gemm_tc: the unary epilogue knows {sorted(UNARY_ACTIVATIONS)} and takes no partials, cap, gate or scale")
+        out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype, device=a.device)
+        lib = build.load("gemm_tc")
+        _check(lib, lib.tb_gemm_tc_unary(_ptr(a), _ptr(w), _ptr(out), c_int(code(out_dtype)), c_int(a.shape[0]), c_int(w.shape[0]),
+                                         c_int(a.shape[1]), c_longlong(a.stride(0)), c_longlong(w.stride(0)),
+                                         c_longlong(out.stride(0)), c_int(1), _stream()), "gemm_tc")
+        return out
     if not gemm_tc_takes(a, w):
         raise KernelError(f"gemm_tc does not take a {tuple(a.shape)}/{a.stride()} {a.dtype}, "
                           f"w {tuple(w.shape)}/{w.stride()} {w.dtype}")
@@ -765,6 +916,18 @@ def gemm_tc_error() -> int:
     """Reads and clears the tensor-core GEMM's error word (synchronises): 0, or the role whose
     bounded wait ran out (1 loader, 2 MMA issuer, 3 epilogue; 4 to 6 the same roles of the kernel on pairs of SMs)."""
     return int(build.load("gemm_tc").tb_gemm_tc_error())
+
+
+def attn_padded_head(dtype: torch.dtype, n: int) -> int:
+    """The head size at which keys and values of up to ``n`` numbers a head are stored and attended to: in bfloat16 the
+    next size that the tensor-core kernels of both prefill and decode take (64, 128, 256), beyond that the next multiple
+    of 16; in float32 ``n`` itself (the generic kernel takes any size)."""
+    if dtype != torch.bfloat16:
+        return n
+    for size in (64, 128, 256):
+        if n <= size:
+            return size
+    return (n + 15) // 16 * 16
 
 
 def attn_prefill_takes(dtype: torch.dtype, head_dim: int) -> bool:
@@ -1360,12 +1523,14 @@ class _MoeRouteArgs(ctypes.Structure):
     _fields_ = [("logits", c_void_p), ("splits", c_int), ("split_stride", c_longlong), ("row_stride", c_longlong),
                 ("correction", c_void_p), ("has_gate", c_int), ("idx", c_void_p), ("weight", c_void_p), ("gate", c_void_p),
                 ("n_tokens", c_int), ("W", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int),
-                ("group_top", c_int), ("weight_eps", c_float)]
+                ("group_top", c_int), ("weight_eps", c_float), ("softmax", c_int), ("out_scale", c_float)]
 
 
 def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Tensor], has_gate: bool,
-              top: int, groups: int, keep: int, group_top: int, weight_eps: float):
-    """Sigmoid-scored routing with groups (see moe.cu) from the router's logits: float32 [T, >= experts (+ 1)] or
+              top: int, groups: int, keep: int, group_top: int, weight_eps: float, score: str = "sigmoid",
+              out_scale: float = 1.0):
+    """Routing with groups (see moe.cu; ``score`` "sigmoid" or "softmax" over all experts; the weights come times
+    ``out_scale``) from the router's logits: float32 [T, >= experts (+ 1)] or
     partial sums [splits, T, ...] of the router product (column ``experts`` is the shared expert's gate product if
     ``has_gate``).  Returns (chosen experts int32 [T, top], their weights float32 [T, top], the shared expert's gate
     float32 [T] or None)."""
@@ -1388,6 +1553,9 @@ def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Ten
     a.idx = idx.data_ptr(); a.weight = weight.data_ptr(); a.gate = gate.data_ptr() if gate is not None else None
     a.n_tokens = T; a.W = 0; a.E = E; a.top = top; a.groups = groups; a.keep = keep; a.group_top = group_top
     a.weight_eps = weight_eps
+    if score not in ("sigmoid", "softmax"):
+        raise KernelError(f"moe_route: scores are 'sigmoid' or 'softmax', not '{score}'")
+    a.softmax = int(score == "softmax"); a.out_scale = out_scale
     lib = build.load("moe")
     _check(lib, lib.tb_moe_route(ctypes.byref(a), _stream()), "moe_route")
     return idx, weight, gate
@@ -1402,12 +1570,13 @@ class _MoePadArgs(ctypes.Structure):
                 ("P", c_int), ("E", c_int), ("max_rows", c_int)]
 
 
-def _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out):
+def _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out, ungated=False):
     """The experts' products on the tcgen05 kernel: the pairs ordered by expert, each expert's stretch padded to whole
-    tiles of 128 rows (see moe.cu and gemm_tc.cu's grouped mode).  Shapes depend on the sizes only."""
+    tiles of 128 rows (see moe.cu and gemm_tc.cu's grouped mode).  Shapes depend on the sizes only.  ``ungated``:
+    ``gate_up_w`` holds the up rows alone and the first product's epilogue is relu(u)^2."""
     T, W = x.shape
     E, ff2 = gate_up_w.shape[0], gate_up_w.shape[1]
-    ff = ff2 // 2
+    ff = ff2 if ungated else ff2 // 2
     top = idx.shape[1]
     P = T * top
     max_rows = ((P + 127) // 128 + min(E, P)) * 128
@@ -1424,9 +1593,14 @@ def _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out):
     act = torch.empty((max_rows, ff), dtype=x.dtype, device=x.device)
     y = torch.empty((max_rows, W), dtype=torch.float32, device=x.device)
     gl = build.load("gemm_tc")
-    _check(gl, gl.tb_gemm_tc_grouped(_ptr(xs), _ptr(gate_up_w), _ptr(act), c_int(code(x.dtype)), c_int(max_rows), c_int(ff2),
-                                     c_int(E), c_int(W), c_longlong(W), c_longlong(W), c_longlong(ff), _ptr(tile_group),
-                                     c_int(ACTIVATIONS["silu"]), _stream()), "gemm_tc_grouped")
+    if ungated:
+        _check(gl, gl.tb_gemm_tc_grouped_unary(_ptr(xs), _ptr(gate_up_w), _ptr(act), c_int(code(x.dtype)), c_int(max_rows), c_int(ff),
+                                               c_int(E), c_int(W), c_longlong(W), c_longlong(W), c_longlong(ff), _ptr(tile_group),
+                                               c_int(1), _stream()), "gemm_tc_grouped")
+    else:
+        _check(gl, gl.tb_gemm_tc_grouped(_ptr(xs), _ptr(gate_up_w), _ptr(act), c_int(code(x.dtype)), c_int(max_rows), c_int(ff2),
+                                         c_int(E), c_int(W), c_longlong(W), c_longlong(W), c_longlong(ff), _ptr(tile_group),
+                                         c_int(ACTIVATIONS["silu"]), _stream()), "gemm_tc_grouped")
     _check(gl, gl.tb_gemm_tc_grouped(_ptr(act), _ptr(down_w), _ptr(y), c_int(code(torch.float32)), c_int(max_rows), c_int(W),
                                      c_int(E), c_int(ff), c_longlong(ff), c_longlong(ff), c_longlong(W), _ptr(tile_group),
                                      c_int(-1), _stream()), "gemm_tc_grouped")
@@ -1453,7 +1627,7 @@ def _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out):
     """The experts' products with the pairs grouped by expert (bfloat16, tensor cores; see moe.cu).  The grid holds the
     most tiles there can be, so nothing the host does depends on which experts were chosen."""
     T, W = x.shape
-    E, ff = gate_w.shape[0], gate_w.shape[1]
+    E, ff = up_w.shape[0], up_w.shape[1]
     top = idx.shape[1]
     P = T * top
     max_tiles = (P + 127) // 128 + min(E, P)          # tiles of 128 pairs; every expert may end with one that is not full
@@ -1469,7 +1643,7 @@ def _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out):
     _check(lib, lib.tb_moe_group(ctypes.byref(g), _stream()), "moe_group")
     a = _MoeGroupedArgs()
     a.x = x.data_ptr(); a.x_stride = x.stride(0)
-    a.gate_w = gate_w.data_ptr(); a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
+    a.gate_w = gate_w.data_ptr() if gate_w is not None else None; a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
     a.perm = perm.data_ptr(); a.tile_expert = te.data_ptr(); a.tile_row0 = tr0.data_ptr(); a.tile_rows = trn.data_ptr()
     a.n_tiles = nt.data_ptr(); a.weight = weight.data_ptr(); a.act = act.data_ptr(); a.pair_out = pair_out.data_ptr()
     a.W = W; a.ff = ff; a.top = top
@@ -1483,22 +1657,26 @@ class _MoeExpertArgs(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("x_stride", c_longlong), ("gate_w", c_void_p), ("up_w", c_void_p), ("down_w", c_void_p),
                 ("idx", c_void_p), ("weight", c_void_p), ("act", c_void_p), ("shared", c_void_p), ("shared_splits", c_int),
                 ("shared_split_stride", c_longlong), ("gate", c_void_p), ("out", c_void_p),
-                ("n_tokens", c_int), ("W", c_int), ("ff", c_int), ("top", c_int)]
+                ("n_tokens", c_int), ("W", c_int), ("ff", c_int), ("top", c_int), ("ungated", c_int)]
 
 
-def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor, idx: torch.Tensor,
+def moe_experts(x: torch.Tensor, gate_w: Optional[torch.Tensor], up_w: torch.Tensor, down_w: torch.Tensor, idx: torch.Tensor,
                 weight: torch.Tensor, shared: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                 gate_up_w: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The weighted sum of every token's chosen experts ``down_e(silu(gate_e x) * up_e x)`` plus ``gate[t] * shared[t]``
     (``shared`` float32 partial sums [splits, T, W]); returns float32 [T, W].  Expert matrices: ``gate_w``, ``up_w``
     [E, ff, W] and ``down_w`` [E, W, ff] of x's dtype; ``gate_up_w`` [E, 2 ff, W]: every expert's gate and up rows
-    interleaved (``interleave_gate_up``), which lets many tokens run on the tcgen05 product."""
+    interleaved (``interleave_gate_up``), which lets many tokens run on the tcgen05 product.  ``gate_w`` None: the
+    experts have no gate matrix and are ``down_e(relu(up_e x)^2)``."""
     _cuda(x, gate_w, up_w, down_w, idx, weight, shared, gate, gate_up_w)
     _rows_contig(x, "moe: x")
     T, W = x.shape
-    E, ff = gate_w.shape[0], gate_w.shape[1]
+    E, ff = up_w.shape[0], up_w.shape[1]
     top = idx.shape[1]
+    ungated = gate_w is None
     for name, t, shape in (("gate", gate_w, (E, ff, W)), ("up", up_w, (E, ff, W)), ("down", down_w, (E, W, ff))):
+        if t is None:
+            continue
         if tuple(t.shape) != shape or t.dtype != x.dtype or not t.is_contiguous():
             raise KernelError(f"moe: the experts' {name} matrices must be contiguous {x.dtype} {shape}, got {tuple(t.shape)} {t.dtype}")
     if shared is not None:
@@ -1510,13 +1688,16 @@ def moe_experts(x: torch.Tensor, gate_w: torch.Tensor, up_w: torch.Tensor, down_
     out = torch.empty((T, W), dtype=torch.float32, device=x.device)
     if x.dtype == torch.bfloat16 and T * top >= MOE_GROUPED_FROM and W % 8 == 0 and ff % 8 == 0 and x.stride(0) % 8 == 0 \
             and x.data_ptr() % 16 == 0:
+        if ungated and T * top >= MOE_TCGEN05_FROM:
+            return _moe_grouped_tc(x, up_w, down_w, idx, weight, shared, gate, out, ungated=True)
         if gate_up_w is not None and T * top >= MOE_TCGEN05_FROM and ff % 16 == 0:
             return _moe_grouped_tc(x, gate_up_w, down_w, idx, weight, shared, gate, out)
         return _moe_grouped(x, gate_w, up_w, down_w, idx, weight, shared, gate, out)
     act = torch.empty((T * top, ff), dtype=x.dtype, device=x.device)
     a = _MoeExpertArgs()
     a.x = x.data_ptr(); a.x_stride = x.stride(0)
-    a.gate_w = gate_w.data_ptr(); a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
+    a.gate_w = gate_w.data_ptr() if gate_w is not None else None; a.up_w = up_w.data_ptr(); a.down_w = down_w.data_ptr()
+    a.ungated = int(ungated)
     a.idx = idx.data_ptr(); a.weight = weight.data_ptr(); a.act = act.data_ptr()
     a.shared = shared.data_ptr() if shared is not None else None
     a.shared_splits = shared.shape[0] if shared is not None else 0

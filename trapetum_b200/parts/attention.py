@@ -32,6 +32,23 @@ the attention kernel (``ops.headnorm_kv``), all in 32-bit:
 * ``q_temp`` ``{"coef": c, "every": n}``: the query at position p is multiplied by
   ``1 + c * ln(floor((p + 1) / n) + 1)``.
 
+Four more options serve mixers that norm q and k over the WHOLE projection; they
+go with a rotation or with none, and run in one kernel between the projection and
+the attention kernel (``ops.projnorm_kv``), all in 32-bit:
+
+* ``proj_norm`` ``{"q": name, "k": name, "eps": e}``: q (all heads at once) and k are
+  divided by their root mean square and multiplied by a weight of the projection's
+  size, before the rotation;
+* ``head_temp`` (a tensor name, one number per head): head h's scores are multiplied
+  by it (applied to the query, in which the score is linear);
+* ``value_dim``: values of another size than the keys.  Keys and values are then
+  stored with one padded head size (``ops.attn_padded_head``), zeros in the padding,
+  which changes neither a score nor the kept part of the output; the output
+  projection gets zero columns to match;
+* ``out_gate`` (a tensor name, [heads, hidden]): head h's output is multiplied by
+  ``sigmoid(G x)[h]`` before the output projection; its rows ride in the fused
+  projection.
+
 The three projections are fused into one matrix when the weights are bound, so
 a step runs one product for q, k and v.
 """
@@ -88,15 +105,38 @@ class Attention(Mixer):
         if self.prepared and (self.position.rotary_table() != (None, 0) or self.bias_names or self.q_norm or self.k_norm):
             raise ValueError("attention: 'v' None, 'head_unit_norm' and 'q_temp' go with position 'none' and without "
                              "biases or weighted head norms")
+        self.vd = int(p.get("value_dim") or self.hd)
+        pn = dict(p.get("proj_norm") or {})
+        self.proj_norm_names = {key: pn[key] for key in ("q", "k") if pn.get(key)}
+        self.proj_norm_eps = float(pn.get("eps", 0.0))
+        self.head_temp_name = p.get("head_temp")
+        self.out_gate_name = p.get("out_gate")
+        self.projected = bool(self.proj_norm_names or self.head_temp_name or self.out_gate_name or self.vd != self.hd)
+        if self.projected:
+            if self.prepared or self.bias_names or self.q_norm or self.k_norm or self.softcap:
+                raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim' and 'out_gate' go without biases, head "
+                                 "norms, a cap, 'v' None, 'head_unit_norm' and 'q_temp'")
+            if self.position.rotary_table() is None:
+                raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim' and 'out_gate' go with a rotate-half "
+                                 "rotation or with no position encoding")
+            self.pad = ops.attn_padded_head(rt.dtype, max(self.hd, self.vd))
+        self.wq_norm = self.wk_norm = self.head_temp = self.w_o_padded = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {
             self._name("q"): TensorSpec((self.qd, self.hidden)),
             self._name("k"): TensorSpec((self.kvd, self.hidden)),
-            self._name("o"): TensorSpec((self.hidden, self.qd)),
+            self._name("o"): TensorSpec((self.hidden, self.n_heads * self.vd)),
         }
         if not self.v_from_k:
-            specs[self._name("v")] = TensorSpec((self.kvd, self.hidden))
+            specs[self._name("v")] = TensorSpec((self.n_kv * self.vd, self.hidden))
+        for key, n in (("q", self.qd), ("k", self.kvd)):
+            if key in self.proj_norm_names:
+                specs[self.prefix + self.proj_norm_names[key]] = TensorSpec((n,), "gain")
+        if self.head_temp_name:
+            specs[self.prefix + self.head_temp_name] = TensorSpec((self.n_heads,), "gain")
+        if self.out_gate_name:
+            specs[self.prefix + self.out_gate_name] = TensorSpec((self.n_heads, self.hidden))
         sizes = {"q": self.qd, "k": self.kvd, "v": self.kvd, "o": self.hidden}
         for key, name in self.bias_names.items():
             specs[self.prefix + name] = TensorSpec((sizes[key],))
@@ -108,9 +148,27 @@ class Attention(Mixer):
     def bind(self, tensors) -> None:
         mats = [tensors[self._name(n)] for n in (("q", "k") if self.v_from_k else ("q", "k", "v"))]
         q = mats[0]
+        if self.projected:
+            if self.out_gate_name:
+                mats.append(tensors[self.prefix + self.out_gate_name])
+            n = sum(m.shape[0] for m in mats)
+            mats.append(torch.zeros((-n % 16, self.hidden), dtype=q.dtype, device=q.device))     # whole tiles of weight rows
+            # short vectors that enter 32-bit arithmetic: kept in 32 bits (exact for what a file stores in 16)
+            if "q" in self.proj_norm_names:
+                self.wq_norm = tensors[self.prefix + self.proj_norm_names["q"]].float().contiguous()
+            if "k" in self.proj_norm_names:
+                self.wk_norm = tensors[self.prefix + self.proj_norm_names["k"]].float().contiguous()
+            if self.head_temp_name:
+                self.head_temp = tensors[self.prefix + self.head_temp_name].float().contiguous()
+            w_o = tensors[self._name("o")]
+            if self.pad != self.vd:
+                wide = torch.zeros((self.hidden, self.n_heads, self.pad), dtype=w_o.dtype, device=w_o.device)
+                wide[:, :, :self.vd] = w_o.view(self.hidden, self.n_heads, self.vd)
+                w_o = wide.view(self.hidden, self.n_heads * self.pad).contiguous()
+            self.w_o_padded = w_o
         dt = q.dtype if all(m.dtype == q.dtype for m in mats) else torch.float32
         self.w_qkv = torch.cat([m.to(dt) for m in mats], dim=0).contiguous()
-        self.w_o = tensors[self._name("o")]
+        self.w_o = self.w_o_padded if self.projected else tensors[self._name("o")]
         self.position.bind(tensors)
         if any(key in self.bias_names for key in "qkv"):
             # one bias row for the fused projection, 32-bit; a projection without a bias of its own gets zeros
@@ -148,6 +206,15 @@ class Attention(Mixer):
         return part
 
     def kernel_files(self):
+        if self.projected:
+            fast = ("projnorm_kv",)
+            if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.pad):
+                fast += ("attention_decode",)
+            if ops.attn_prefill_tc_takes(self.rt.dtype, self.pad):
+                fast += (ops.attn_prefill_tc_lib(self.pad),)
+            elif ops.attn_prefill_takes(self.rt.dtype, self.pad):
+                fast += (ops.attn_prefill_lib(self.pad),)
+            return linear_kernels(self.rt.dtype) + ("attention_simt",) + fast
         fast = ("attention_decode",) if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.hd) else ()
         if self.prepared:
             fast += ("headnorm_kv",)
@@ -163,10 +230,12 @@ class Attention(Mixer):
         return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",) + fast
 
     def cache_need(self):
-        return KVNeed(self.n_kv, self.hd, self.window)
+        return KVNeed(self.n_kv, self.pad if self.projected else self.hd, self.window)
 
     def forward(self, x, ctx, line):
         dt = self.rt.dtype
+        if self.projected:
+            return self._forward_projected(x, ctx, line)
         if self.prepared:
             return self._forward_prepared(x, ctx, line)
         if line.owner:
@@ -229,6 +298,33 @@ class Attention(Mixer):
                                 self.hd, self.scale, self.softcap, self.window or 0, line.ring_rows, ctx.len_bucket,
                                 ctx.uneven)
         return self._out(o)
+
+
+    def _forward_projected(self, x, ctx, line):
+        """The path of ``proj_norm`` / ``head_temp`` / ``value_dim`` / ``out_gate``: the fused projection as 32-bit partial
+        sums, one kernel that norms, weighs, rotates, pads, rounds, fills the cache and takes the gate's sigmoid, then the
+        same attention kernels as every other mixer at the padded head size."""
+        dt = self.rt.dtype
+        if not line.owner:
+            raise NotImplementedError("attention: a mixer with a projection-wide norm that reads another call's cache is not built")
+        H, G, D = self.n_heads, self.n_kv, self.pad
+        inv_freq, rotary = self.position.rotary_table()
+        part = linear_partials(x, self.w_qkv)
+        qkv, gate = ops.projnorm_kv(part, H, G, self.hd, self.vd, D, dt, self.wq_norm, self.wk_norm, self.proj_norm_eps,
+                                    self.head_temp, rotary, inv_freq, bool(self.out_gate_name), ctx.positions,
+                                    ctx.token_seq, ctx.len_after, line.k, line.v, line.page_table, line.ring_rows)
+        q = qkv[:, :H * D]
+        k = qkv[:, H * D:(H + G) * D]
+        v = qkv[:, (H + G) * D:]
+        if ctx.is_prefill:
+            o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, H, G, D, self.scale, 0.0, self.window or 0,
+                                 ctx.max_seq_len, ctx.seq_lens, ctx.memo)
+        else:
+            o = ops.attn_decode(q, line.k, line.v, line.page_table, ctx.len_after, H, G, D, self.scale, 0.0,
+                                self.window or 0, line.ring_rows, ctx.len_bucket, ctx.uneven)
+        if gate is not None:
+            ops.head_gate(o, gate, H)
+        return linear_partials(o, self.w_o)
 
 
 register_part("mixer", "attention", Attention)

@@ -19,6 +19,13 @@ the way in, and both sublayers read the stream itself:
 ``side`` input (a feed-forward that may look at the step's token ids),
 ``h <- h + side_norm(side(h))``.
 
+``parallel``: one norm, both sublayers read its output, and their outputs are
+added together, times ``scale`` (1 if absent):
+
+    x = norm(h);  h += scale * (mixer(x) + feed_forward(x))
+
+(without a feed-forward: ``h += scale * mixer(x)``).
+
 A block only talks to the :class:`~trapetum_b200.parts.stream.ResidualStream`,
 which decides how additions and norms are fused.
 """
@@ -124,6 +131,24 @@ class PostNormBlock(_NormedBlock):
             stream.add_normed(self.side.forward(stream.read(dt), ctx), self.norms["side_norm"])
 
 
+class ParallelBlock(_NormedBlock):
+    """Parameters: ``norm`` (the one norm's spec) and ``scale``."""
+    NORMS = ("norm",)
+
+    def __init__(self, params, prefix, rt, mixer, feed_forward):
+        super().__init__(params, prefix, rt, mixer, feed_forward)
+        self.scale = float(params.get("scale", 1.0))
+        self.has_ffn = not getattr(feed_forward, "absent", False)
+
+    def forward(self, stream, ctx, cache) -> None:
+        x = stream.normed(self.norms["norm"], self.rt.dtype)
+        branches = [self.mixer.forward(x, ctx, cache)]
+        if self.has_ffn:
+            branches.append(self.feed_forward.forward(x, ctx))
+        stream.add_scaled(branches, self.scale)
+
+
+register_part("block", "parallel", ParallelBlock)
 register_part("block", "post_norm", PostNormBlock)
 register_part("block", "sandwich", SandwichBlock)
 register_part("block", "pre_norm", PreNormBlock)

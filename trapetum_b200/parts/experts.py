@@ -8,11 +8,15 @@ others' choice scores count as minus infinity); the ``top`` largest choice score
 their ``s`` (without the correction) divided by their sum plus ``weight_eps``.  The output is the weighted sum
 of the winners' outputs, plus, if there is a shared expert, ``sigmoid(g . x)`` times its output for every token.
 
+Two more forms of the same part: ``score`` "softmax" takes ``s = softmax(z)`` over all experts, and ``gated``
+False makes the experts ``down_e(act(up_e x))`` with a unary activation ("relu2", the square of relu) and no gate
+matrix; the shared expert is then of that form too.  ``route_scale`` multiplies the winners' weights.
+
 Parameters (none is fixed in code): ``hidden_size``, ``experts``, ``top``, ``intermediate_size``, ``activation``
 ("silu"), ``score`` ("sigmoid"), ``groups``, ``keep_groups``, ``group_score_of``, ``weight_eps``, the tensor names
 ``router``, ``correction`` (None: no correction), ``expert`` (a pattern with ``{}`` for the expert's number) with
 ``gate``, ``up``, ``down`` below it, and ``shared``: None or ``{"intermediate_size", "gate", "up", "down",
-"token_gate"}`` (``token_gate`` None: the shared expert is added as it is).
+"token_gate"}`` (``token_gate`` None: the shared expert is added as it is; no ``gate`` with ungated experts).
 """
 from __future__ import annotations
 
@@ -23,7 +27,7 @@ import torch
 from ..csrc import ops
 from ..weights.loader import TensorSpec
 from .base import FeedForward, register_part
-from .feed_forward import GatedMLP
+from .feed_forward import GatedMLP, PlainMLP
 from .linear import kernel_files as linear_kernels
 from .linear import linear_partials
 
@@ -42,17 +46,26 @@ class RoutedExperts(FeedForward):
         self.keep = int(p.get("keep_groups") or self.groups)
         self.group_top = int(p.get("group_score_of") or 1)
         self.weight_eps = float(p.get("weight_eps") or 0.0)
-        if p.get("activation", "silu") != "silu" or p.get("score", "sigmoid") != "sigmoid":
-            raise ValueError("routed_experts: the kernels know the silu activation and sigmoid scores")
+        self.gated = bool(p.get("gated", True))
+        self.activation = p.get("activation", "silu")
+        self.score = p.get("score", "sigmoid")
+        self.route_scale = float(p.get("route_scale", 1.0))
+        if self.activation != ("silu" if self.gated else "relu2") or self.score not in ("sigmoid", "softmax"):
+            raise ValueError("routed_experts: the kernels know gated experts with silu, ungated experts with relu2, and "
+                             "sigmoid or softmax scores")
         if not (1 <= self.top <= self.E) or self.E % self.groups or not (1 <= self.keep <= self.groups) \
                 or self.keep * (self.E // self.groups) < self.top:
             raise ValueError(f"routed_experts: experts={self.E} top={self.top} groups={self.groups} keep={self.keep}")
-        self.shared: Optional[GatedMLP] = None
+        self.shared = None
         self.shared_gate_name = None
         sh = p.get("shared")
-        if sh:
+        if sh and self.gated:
             self.shared = GatedMLP({"hidden_size": self.hidden, "intermediate_size": int(sh["intermediate_size"]),
                                     "activation": "silu", "gate": sh["gate"], "up": sh["up"], "down": sh["down"]}, prefix, rt)
+        elif sh:
+            self.shared = PlainMLP({"hidden_size": self.hidden, "intermediate_size": int(sh["intermediate_size"]),
+                                    "activation": self.activation, "up": sh["up"], "down": sh["down"]}, prefix, rt)
+        if sh:
             self.shared_gate_name = sh.get("token_gate")
 
     def _expert(self, e: int, key: str) -> str:
@@ -63,7 +76,8 @@ class RoutedExperts(FeedForward):
         if self.params.get("correction"):
             specs[self._name("correction")] = TensorSpec((self.E,), "norm")
         for e in range(self.E):
-            specs[self._expert(e, "gate")] = TensorSpec((self.ff, self.hidden))
+            if self.gated:
+                specs[self._expert(e, "gate")] = TensorSpec((self.ff, self.hidden))
             specs[self._expert(e, "up")] = TensorSpec((self.ff, self.hidden))
             specs[self._expert(e, "down")] = TensorSpec((self.hidden, self.ff))
         if self.shared is not None:
@@ -75,14 +89,15 @@ class RoutedExperts(FeedForward):
     def bind(self, tensors) -> None:
         router = tensors[self._name("router")]
         self.correction = tensors[self._name("correction")].float().contiguous() if self.params.get("correction") else None
-        dt = tensors[self._expert(0, "gate")].dtype
-        self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous()
+        dt = tensors[self._expert(0, "up")].dtype
+        self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous() \
+            if self.gated else None
         self.w_up = torch.stack([tensors[self._expert(e, "up")].to(dt) for e in range(self.E)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")].to(dt) for e in range(self.E)]).contiguous()
         # for many tokens: every expert's gate and up rows interleaved, as the tensor-core product's gated epilogue
         # wants them (a second copy of those rows; steps of few tokens read the plain ones)
         self.w_gate_up = None
-        if dt == torch.bfloat16 and self.rt.dtype == torch.bfloat16 and self.ff % 16 == 0 and self.hidden % 8 == 0:
+        if self.gated and dt == torch.bfloat16 and self.rt.dtype == torch.bfloat16 and self.ff % 16 == 0 and self.hidden % 8 == 0:
             self.w_gate_up = torch.stack([ops.interleave_gate_up(self.w_gate[e], self.w_up[e]) for e in range(self.E)]).contiguous()
         rows = [router]
         self.has_gate = False
@@ -102,7 +117,7 @@ class RoutedExperts(FeedForward):
     def forward(self, x, ctx):
         logits = linear_partials(x, self.w_router)             # 32-bit sums; the routing itself is 32-bit throughout
         idx, weight, gate = ops.moe_route(logits, self.E, self.correction, self.has_gate, self.top, self.groups,
-                                          self.keep, self.group_top, self.weight_eps)
+                                          self.keep, self.group_top, self.weight_eps, self.score, self.route_scale)
         shared = None
         if self.shared is not None:
             shared = self.shared.forward(x, ctx)              # float32 partial sums [splits, T, hidden]

@@ -7,6 +7,9 @@ gate and up matrices are fused into one when the weights are bound.  The
 activation ``clamped_swish`` takes a ``limit`` L and bounds both branches:
 ``g' = min(g, L)``, ``u' = clamp(u, -L, L)``, ``g' sigmoid(1.702 g') (u' + 1)``.
 
+``mlp`` is the form without a gate branch, ``down(act(up(x)))``, with a unary
+activation (``relu2``: the square of relu).
+
 Also here: ``none`` (a layer without a feed-forward) and ``token_gated``, a narrow
 side input that is looked up by token id:
 ``proj(gelu_tanh(gate(x)) * table[token][first_col : first_col + dim])``.
@@ -75,6 +78,41 @@ class GatedMLP(FeedForward):
         return linear_partials(act, self.w_down)
 
 
+class PlainMLP(FeedForward):
+    """``down(act(up(x)))``.  Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (a unary one: "relu2")
+    and the tensor names ``up`` and ``down``.  With many tokens the activation runs in the tensor-core product's
+    epilogue; with few, the product keeps its split-K partial sums and a small kernel adds and activates them."""
+    graph_safe = True          # every launch depends on device data only
+
+    def __init__(self, params, prefix, rt):
+        super().__init__(params, prefix, rt)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = params["activation"]
+        if self.activation not in ops.UNARY_ACTIVATIONS:
+            raise ValueError(f"mlp: unknown activation '{self.activation}' (known: {sorted(ops.UNARY_ACTIVATIONS)})")
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {self._name("up"): TensorSpec((self.inter, self.hidden)),
+                self._name("down"): TensorSpec((self.hidden, self.inter))}
+
+    def bind(self, tensors) -> None:
+        self.w_up = tensors[self._name("up")]
+        self.w_down = tensors[self._name("down")]
+
+    def kernel_files(self):
+        return linear_kernels(self.rt.dtype) + ("activation",)
+
+    def forward(self, x, ctx):
+        if x.shape[0] > 128 and x.dtype == torch.bfloat16 and self.w_up.dtype == torch.bfloat16 and ops.gemm_tc_takes(x, self.w_up):
+            act = ops.gemm_tc(x, self.w_up, self.rt.dtype, unary_act=self.activation)
+        else:
+            act = ops.unary_act(linear_partials(x, self.w_up), self.activation, self.rt.dtype)
+        return linear_partials(act, self.w_down)
+
+
 class NoFeedForward(FeedForward):
     """A layer without a feed-forward: arrangements that allow it look at ``absent`` and skip the branch."""
     graph_safe = True
@@ -125,5 +163,6 @@ class TokenGated(FeedForward):
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
+register_part("feed_forward", "mlp", PlainMLP)
 register_part("feed_forward", "none", NoFeedForward)
 register_part("feed_forward", "token_gated", TokenGated)

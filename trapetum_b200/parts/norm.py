@@ -4,6 +4,13 @@
 stored weights at export (model/export_gemma.py:25-26) and then runs the plain
 form (runtime/cuda/codebook_gemv.cu:192-202); here the raw weight is kept and
 the sum is made in the kernel in 32-bit.
+
+``scalar`` selects the norm whose weight is ONE number for all coordinates
+(stored as a tensor without axes): ``y = x * rsqrt(mean(x^2) + eps) * g``.  The
+number is spread over the row once, when the weights are bound, so every kernel
+of the vector form serves it.  :meth:`RMSNorm.add_scaled_apply` is the fused form
+``h += scale * (a + b); y = norm(h)`` for arrangements whose sublayers read one
+normed input and add their outputs together.
 """
 from __future__ import annotations
 
@@ -22,14 +29,22 @@ class RMSNorm(Norm):
         self.size = int(params["size"])
         self.eps = float(params["eps"])
         self.offset = 1.0 if params.get("unit_offset") else 0.0
+        self.scalar = bool(params.get("scalar"))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         # "norm": drawn around 0 in random mode (the (1 + w) form); "gain": around 1 (a plain weight)
-        return {self._name("weight"): TensorSpec((self.size,), self.params.get("role", "norm"))}
+        role = self.params.get("role", "gain" if self.scalar else "norm")
+        return {self._name("weight"): TensorSpec(() if self.scalar else (self.size,), role)}
 
     def bind(self, tensors) -> None:
         self.weight = tensors[self._name("weight")]
+        if self.scalar:      # one number for the whole row: spread once, in 32 bits (exact for what a file stores in 16)
+            self.weight = self.weight.float().reshape(1).expand(self.size).contiguous()
+
+    def add_scaled_apply(self, h: torch.Tensor, branches, scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+        """``h += scale * (sum of the branch outputs)`` in place, returns ``norm(h)``; one kernel."""
+        return ops.add_scaled_rmsnorm(h, branches, scale, self.weight, self.eps, self.offset, out_dtype)
 
     def kernel_files(self):
         return ("norm",)

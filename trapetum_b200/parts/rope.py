@@ -3,7 +3,8 @@
 For each head and i in [0, R/2): ``angle = pos * theta^(-2i/R)`` and the pair
 ``(x[i], x[i+R/2])`` is rotated by it (runtime/cuda/codebook_gemv.cu:219-230;
 the table of inverse frequencies is made as in model/export_gemma.py:53).  R is
-``rotary_dim`` (the whole head for Gemma-2).  The table is made once, in
+``rotary_dim`` (the whole head for Gemma-2).  ``scaling_factor`` f (1 if absent)
+is linear position scaling: every frequency is divided by f.  The table is made once, in
 32-bit; the kernel multiplies by the position and takes sin and cos in 32-bit.
 The rotation is fused with the cache write, so a mixer hands this part its qkv
 matrix and its cache line in one call.
@@ -27,7 +28,12 @@ class Rope(PositionEncoding):
         if self.rotary_dim % 2 or not (0 < self.rotary_dim <= self.head_dim):
             raise ValueError(f"rope: rotary_dim {self.rotary_dim} must be even and within head_dim {self.head_dim}")
         idx = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
+        self.scaling_factor = float(params.get("scaling_factor") or 1.0)
+        if not self.scaling_factor > 0.0:
+            raise ValueError(f"rope: scaling_factor must be positive, got {self.scaling_factor}")
         self._inv_freq_cpu = 1.0 / (torch.tensor(self.theta, dtype=torch.float32) ** (idx / self.rotary_dim))
+        if self.scaling_factor != 1.0:
+            self._inv_freq_cpu = self._inv_freq_cpu / self.scaling_factor
         self.inv_freq: Optional[torch.Tensor] = None
 
     def bind(self, tensors) -> None:

@@ -38,6 +38,11 @@ class ResidualStream:
         self._flush()
         self._pending = (a, norm, None)
 
+    def add_scaled(self, branches, scale: float) -> None:
+        """h += scale * (sum of one or two branch outputs, float32 or their split-K partial sums)."""
+        self._flush()
+        self._pending = (list(branches), None, ("scaled", float(scale)))
+
     def fold_normed(self, a: torch.Tensor, norm: Norm, alpha: float) -> None:
         """h <- norm(alpha * h + a): the norm after the sum."""
         self._flush()
@@ -45,6 +50,11 @@ class ResidualStream:
 
     def normed(self, norm: Norm, out_dtype: torch.dtype) -> torch.Tensor:
         """norm(h), after whatever addition was still waiting."""
+        if self._pending is not None and isinstance(self._pending[2], tuple):
+            branches, _, (_, scale) = self._pending
+            if hasattr(norm, "add_scaled_apply"):
+                self._pending = None
+                return norm.add_scaled_apply(self.h, branches, scale, out_dtype)      # the scaled sum and the norm in one kernel
         if self._pending is not None and self._pending[2] is None:
             a, post, _ = self._pending
             self._pending = None
@@ -82,7 +92,9 @@ class ResidualStream:
             return
         a, post, alpha = self._pending
         self._pending = None
-        if alpha is not None:
+        if isinstance(alpha, tuple):
+            ops.add_scaled_rmsnorm(self.h, a, alpha[1])
+        elif alpha is not None:
             post.fold(self.h, a, alpha, None)
         elif post is not None:
             post.add_to(self.h, a, None, None)
