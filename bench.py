@@ -20,6 +20,7 @@ MEASURED_PEAKS.json beside this file when the driver wrote it, otherwise from th
 
     python bench.py --design divanex [--sizes small,medium,large] [--batch 8] [--context 2048]
     python bench.py --design lofirax [--sizes small,medium,large] [--batch 8] [--context 2048]
+    python bench.py --design fidepel [--sizes small,medium,large] [--batch 8] [--context 2048]
 
 ``--design divanex`` is a measurement of its own (the default workload and its line stay as they are): Divanex
 models with random weights at a few layer sizes, a 2,048-token prompt and decode steps of ``batch`` sequences
@@ -568,6 +569,236 @@ def lofirax_compare(args, torch):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design fidepel: the design at sizes that resemble real layers, beside Gemma-2 (the closest model of the library:
+# every layer a rotary, windowed, grouped-query attention over the same cache and attention kernels) at equal width,
+# depth, head counts, head size and vocabulary; its experts' kernels beside Lofirax's gated ones at equal sizes
+# ---------------------------------------------------------------------------------------------------------------
+# name -> (value size, window; experts, top, expert ff, groups, kept groups, shared ff); width, depth, heads, kv heads,
+#          head size and vocabulary are DESIGN_SIZES'
+FIDEPEL_SIZES = {"small": (128, 4096, 16, 4, 512, 4, 2, 1024),
+                 "medium": (128, 4096, 32, 4, 1024, 8, 4, 2048),
+                 "large": (128, 4096, 32, 4, 2048, 8, 4, 4096)}
+
+
+def fidepel_config(size):
+    W, L, H, G, d, _, _, _, _, V = DESIGN_SIZES[size]
+    vd, window, E, top, eff, groups, keep, sff = FIDEPEL_SIZES[size]
+    layer = {"type": "attention",
+             "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": vd, "scale": d ** -0.5, "mask": {"size": window},
+                       "rot": {"dims": d, "base": 10000.0, "scaling": {"factor": 2.0}}},
+             "mlp": {"kind": "moe", "expert": {"ff": eff},
+                     "router": {"experts": E, "top": top, "scale": 2.0, "groups": {"count": groups, "keep": keep}},
+                     "shared": {"ff": sff}}}
+    # the first two layers run twice: L layer runs from L - 2 layers
+    return {"architecture": "Fidepel", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "loop": {"start": 0, "stop": 2, "times": 2}, "layers": [layer for _ in range(L - 2)]}
+
+
+def fidepel_bytes_flops(cfg, tokens, ctx, batch):
+    """(weight bytes a decode step of ``batch`` sequences reads, with every matrix once and of the experts those that
+    ``batch`` tokens are expected to choose; cache bytes per sequence at ``ctx`` tokens; tensor-core FLOPs of one
+    ``tokens``-token prompt)."""
+    W, V = cfg["width"], cfg["vocab"]
+    n = len(cfg["layers"])
+    lp = cfg.get("loop")
+    runs = [1] * n
+    if lp:
+        for i in range(lp["start"], lp["stop"]):
+            runs[i] = lp["times"]
+    wb, cb, fl = V * W, 0, 2 * V * W * tokens
+    for L, r in zip(cfg["layers"], runs):
+        m, f = L["mixer"], L["mlp"]
+        H, G, D, Vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+        per = (H * D + G * (D + Vd) + H) * W + W * H * Vd
+        pad = next((s for s in (64, 128, 256) if max(D, Vd) <= s), (max(D, Vd) + 15) // 16 * 16)
+        seen = min(ctx, (m.get("mask") or {}).get("size") or ctx)
+        cb += r * 2 * G * pad * seen * 2
+        span = min(tokens, (m.get("mask") or {}).get("size") or tokens)
+        pairs = span * (span + 1) // 2 + (tokens - span) * span          # (query, key) pairs that a window leaves
+        fl += r * 2 * H * (D + Vd) * pairs
+        used = per
+        if f:
+            E, top = f["router"]["experts"], f["router"]["top"]
+            one = 2 * f["expert"]["ff"] * W
+            sh = 2 * f["shared"]["ff"] * W if f.get("shared") else 0
+            used = per + E * W + sh + top * one
+            per += E * W + sh + one * E * (1.0 - (1.0 - top / E) ** batch)
+        wb += per
+        fl += r * 2 * tokens * used
+    return int(2 * wb), cb, fl, 0
+
+
+def fidepel_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
+    """The design's own kernels alone, each beside the like kernel of the closest model: microseconds, algorithmic
+    bytes (or FLOPs) and the fraction of the roofline.  One prompt of ``tokens`` tokens."""
+    from trapetum_b200.csrc import ops
+    W, _, H, G, d, ff, _, _, _, _ = DESIGN_SIZES[size]
+    vd, window, E, top, eff, groups, keep, sff = FIDEPEL_SIZES[size]
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    T = tokens
+    out = {}
+    tc_peak = peaks()[1]
+
+    def rec(name, us, nbytes, like=None, tensor_flops=0.0):
+        t_mem, t_tc = nbytes / (hbm_gbs * 1e9) * 1e6, tensor_flops / (tc_peak * 1e12) * 1e6
+        best = max(t_mem, t_tc)
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(best, 1), "frac": round(best / us, 3),
+                     "bound": "tensor" if best == t_tc else "hbm"}
+        if like:
+            out[name]["like"] = like
+    f32 = lambda *s: torch.randn(*s, device=dev)
+    pos = torch.arange(T, device=dev).int()
+    tseq = torch.zeros(T, device=dev).int()
+    la = torch.tensor([T], device=dev).int()
+    ss = torch.tensor([0, T], device=dev).int()
+    # ---- the scaled sum of both branches with the next layer's norm; beside the sum of one branch with two norms
+    h, a, b = f32(T, W), f32(1, T, W), f32(1, T, W)
+    w32, wbf = torch.ones(W, device=dev), torch.ones(W, device=dev).to(bf)
+    rec("add_scaled_rmsnorm (two branches)", _median_us(torch, lambda: ops.add_scaled_rmsnorm(h, [a, b], 0.5, w32, 1e-6, 0.0, bf), flush),
+        T * W * 18, like="add_rmsnorm")
+    rec("add_rmsnorm", _median_us(torch, lambda: ops.add_rmsnorm(h, a, wbf, 1e-5, 0.0, wbf, 1e-5, 0.0, bf), flush), T * W * 14)
+    # ---- what stands between the fused projection and the attention kernel
+    D = ops.attn_padded_head(bf, max(d, vd))
+    pages = (T + 63) // 64
+    kp = torch.zeros(pages, G, 64, D, dtype=bf, device=dev)
+    vp = torch.zeros_like(kp)
+    table = torch.arange(pages, device=dev).int().view(1, pages)
+    in_w = (H * d + G * (d + vd) + H + 15) // 16 * 16
+    part = f32(1, T, in_w)
+    wq, wk, temp = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev), torch.ones(H, device=dev)
+    inv = torch.rand(d // 2, device=dev)
+    rec("projnorm_kv", _median_us(torch, lambda: ops.projnorm_kv(part, H, G, d, vd, D, bf, wq, wk, 1e-6, temp, d, inv, True, pos, tseq, la,
+                                                                 kp, vp, table, 0), flush),
+        part.numel() * 4 + T * (H + 2 * G) * D * 2 + T * 2 * G * D * 2, like="rope_kv")
+    qkv = torch.randn(T, (H + 2 * G) * d, device=dev).to(bf)
+    kp2 = torch.zeros(pages, G, 64, d, dtype=bf, device=dev)
+    vp2 = torch.zeros_like(kp2)
+    rec("rope_kv", _median_us(torch, lambda: ops.rope_kv(qkv, H, G, d, d, inv, pos, tseq, la, kp2, vp2, table, 0), flush),
+        T * (H + 2 * G) * d * 2 * 2 + T * 2 * G * d * 2)
+    o, gate = torch.randn(T, H * D, device=dev).to(bf), torch.rand(T, H, device=dev)
+    rec("head_gate", _median_us(torch, lambda: ops.head_gate(o, gate, H), flush), T * H * D * 4 + T * H * 4, like="add_rmsnorm")
+    # ---- causal attention of the prompt: the design's and the closest model's are one kernel
+    rec("attention (prefill)",
+        _median_us(torch, lambda: ops.attn_prefill(qkv[:, :H * d], qkv[:, H * d:(H + G) * d], qkv[:, (H + G) * d:], ss, tseq, H, G, d,
+                                                   d ** -0.5, 0.0, window, T, [T], {}), flush),
+        T * (H + 2 * G) * d * 2 + T * H * d * 2, tensor_flops=4.0 * H * d * T * (T + 1) / 2)
+    # ---- routing and the experts; beside the gated experts of equal sizes and a dense gated feed-forward
+    x = torch.randn(T, W, device=dev).to(bf)
+    logits = f32(1, T, (E + 15) // 16 * 16)
+    rec("moe_route (softmax)", _median_us(torch, lambda: ops.moe_route(logits, E, None, False, top, groups, keep, 1, 1e-20, "softmax", 2.0), flush),
+        logits.numel() * 4 + T * top * 8, like="moe_route (sigmoid)")
+    corr = f32(E) * .1
+    rec("moe_route (sigmoid)", _median_us(torch, lambda: ops.moe_route(logits, E, corr, False, top, groups, keep, 2, 1e-20), flush),
+        logits.numel() * 4 + T * top * 8)
+    idx, wt, _ = ops.moe_route(logits, E, None, False, top, groups, keep, 1, 1e-20, "softmax", 2.0)
+    gw, uw, dw = (torch.randn(E, a_, b_, device=dev).to(bf) * .02 for a_, b_ in ((eff, W), (eff, W), (W, eff)))
+    rec("experts without a gate (grouped products)", _median_us(torch, lambda: ops.moe_experts(x, None, uw, dw, idx, wt), flush),
+        2 * E * eff * W * 2 + T * W * 2, tensor_flops=2.0 * T * top * 2 * eff * W, like="gated experts (grouped products)")
+    gu = torch.stack([ops.interleave_gate_up(gw[e], uw[e]) for e in range(E)]).contiguous()
+    rec("gated experts (grouped products)", _median_us(torch, lambda: ops.moe_experts(x, gw, uw, dw, idx, wt, gate_up_w=gu), flush),
+        3 * E * eff * W * 2 + T * W * 2, tensor_flops=2.0 * T * top * 3 * eff * W)
+    su, sd = torch.randn(sff, W, device=dev).to(bf) * .02, torch.randn(W, sff, device=dev).to(bf) * .02
+
+    def shared_ff():
+        return ops.gemm_tc(ops.gemm_tc(x, su, bf, unary_act="relu2"), sd, torch.float32, partials=True)
+    rec("shared expert (two products)", _median_us(torch, shared_ff, flush), 2 * sff * W * 2 + T * W * 2,
+        tensor_flops=2.0 * T * 2 * sff * W, like="gated feed-forward (two products)")
+    wgu = ops.interleave_gate_up(torch.randn(sff, W, device=dev).to(bf) * .02, torch.randn(sff, W, device=dev).to(bf) * .02)
+
+    def dense_ff():
+        return ops.gemm_tc(ops.gemm_tc(x, wgu, bf, gated_act="gelu_tanh"), sd, torch.float32, partials=True)
+    rec("gated feed-forward (two products)", _median_us(torch, dense_ff, flush), 3 * sff * W * 2 + T * W * 2,
+        tensor_flops=2.0 * T * 3 * sff * W)
+    # ---- one token for each of 64 sequences at a context of 2,048: what a decode step adds to the closest model's
+    B, ctx = 64, 2048
+    pg = ctx // 64
+    pos1, tseq1 = torch.full((B,), ctx - 1, device=dev).int(), torch.arange(B, device=dev).int()
+    la1 = torch.full((B,), ctx, device=dev).int()
+    kp3 = torch.randn(B * pg, G, 64, D, device=dev).to(bf)
+    vp3 = torch.randn(B * pg, G, 64, D, device=dev).to(bf)
+    tab = torch.arange(B * pg, device=dev).int().view(B, pg)
+    part1 = f32(4, B, in_w)
+    rec("projnorm_kv, one token for each of 64 sequences",
+        _median_us(torch, lambda: ops.projnorm_kv(part1, H, G, d, vd, D, bf, wq, wk, 1e-6, temp, d, inv, True, pos1, tseq1, la1, kp3, vp3, tab, 0), flush),
+        part1.numel() * 4 + B * (H + 4 * G) * D * 2, like="rope_kv, one token for each of 64 sequences")
+    part2 = f32(4, B, (H + 2 * G) * d)
+    qkv1 = torch.empty(B, (H + 2 * G) * d, dtype=bf, device=dev)
+    kp4 = torch.zeros(B * pg, G, 64, d, dtype=bf, device=dev)
+    vp4 = torch.zeros_like(kp4)
+    rec("rope_kv, one token for each of 64 sequences",
+        _median_us(torch, lambda: ops.rope_kv(qkv1, H, G, d, d, inv, pos1, tseq1, la1, kp4, vp4, tab, 0, partial=part2), flush),
+        part2.numel() * 4 + B * (H + 4 * G) * d * 2)
+    del kp4, vp4
+    qd = torch.randn(B, H * D, device=dev).to(bf)
+    rec("attention (decode)", _median_us(torch, lambda: ops.attn_decode(qd, kp3, vp3, tab, la1, H, G, D, d ** -0.5, 0.0, window, 0, ctx, 0), flush),
+        kp3.numel() * 4)
+    x1 = torch.randn(B, W, device=dev).to(bf)
+    idx1 = torch.stack([torch.randperm(E, device=dev)[:top] for _ in range(B)]).int()
+    wt1 = torch.rand(B, top, device=dev)
+    touched = E * (1.0 - (1.0 - top / E) ** B)
+    rec("experts without a gate, one token for each of 64 sequences", _median_us(torch, lambda: ops.moe_experts(x1, None, uw, dw, idx1, wt1), flush),
+        2 * touched * eff * W * 2, like="gated experts, one token for each of 64 sequences")
+    rec("gated experts, one token for each of 64 sequences", _median_us(torch, lambda: ops.moe_experts(x1, gw, uw, dw, idx1, wt1, gate_up_w=gu), flush),
+        3 * touched * eff * W * 2)
+    return out
+
+
+def fidepel_compare(args, torch):
+    """Prints one JSON line: per size, Fidepel and the Gemma-2 model of equal width, depth, heads and vocabulary
+    (prefill of one 2,048-token prompt, decode at ``batch`` x ``context``), with bytes, FLOPs and roofline fractions,
+    and the design's kernels alone beside their like kernels."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    warmup = max(3, args.warmup)
+    ctx, batch = args.context, args.batch
+    sizes = [s for s in args.sizes.split(",") if s in DESIGN_SIZES]
+    out = {"design": "fidepel", "beside": "gemma2", "sizes": {},
+           "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src},
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "batch": batch, "context": ctx,
+           "timing": "CUDA events; decode: median of five regions of --steps steps; kernels alone: a 256 MB buffer is written "
+                     "between timed launches (larger than L2)"}
+    clocks = ClockSampler()
+    clocks.__enter__()
+    for size in sizes:
+        row = {}
+        for which in ("fidepel", "gemma2"):
+            cfg = fidepel_config(size) if which == "fidepel" else gemma_like(size)
+            V = cfg["vocab"] if which == "fidepel" else cfg["vocab_size"]
+            model = tb.random_model(cfg, 7, 0.02, 0.1, "bfloat16", "cuda:0", host="python")
+            engine = tb.Engine(model, max_tokens=batch * (ctx + 64), max_slots=batch)
+            random_cache(engine)
+            pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=warmup)
+            r = time_decode(engine, torch, [ctx] * batch, args.steps, warmup, V, clocks=clocks)
+            if which == "fidepel":
+                wb, cb, fl, _ = fidepel_bytes_flops(cfg, PREFILL_TOKENS, ctx, batch)
+                nbytes = wb + batch * cb
+            else:
+                nbytes = weight_bytes(cfg) + batch * cache_bytes(cfg, ctx)
+                fl = prefill_flops(cfg, PREFILL_TOKENS)
+            pre_ideal = fl / (bf16_tflops * 1e12)
+            row[which] = {
+                "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tok_s": round(PREFILL_TOKENS * 1e3 / pms, 1),
+                            "tensor_flops": fl, "frac_of_roofline": round(pre_ideal * 1e3 / pms, 4)},
+                "decode": {"ms": r["ms"], "tok_s": round(batch * 1e3 / r["ms"], 1), "bytes": nbytes,
+                           "gbs": round(nbytes / (r["ms"] * 1e-3) / 1e9, 1),
+                           "frac_of_hbm": round(nbytes / (r["ms"] * 1e-3) / 1e9 / hbm_gbs, 4), "launches": r["launches"]},
+            }
+            engine.check_kernels()
+            del engine, model
+            torch.cuda.empty_cache()
+        if not args.no_points:
+            row["kernels_alone"] = fidepel_kernels(torch, size, hbm_gbs)
+        out["sizes"][size] = row
+    clocks.__exit__()
+    out["clocks"] = clocks.summary()
+    out["kernel_errors"] = ops.kernel_errors()
+    print(json.dumps(out))
+    return 0
+
+
 HOST = None              # which host runs the models (None: the library's default, the native host for these models)
 
 
@@ -916,9 +1147,9 @@ def main() -> int:
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
-    ap.add_argument("--design", default=None, choices=["divanex", "lofirax"],
+    ap.add_argument("--design", default=None, choices=["divanex", "lofirax", "fidepel"],
                     help="instead of the bench line: this design at the layer sizes of --sizes beside the library's closest "
-                         "model at equal size (divanex beside Gemma-2, lofirax beside divanex)")
+                         "model at equal size (divanex beside Gemma-2, lofirax beside divanex, fidepel beside Gemma-2)")
     ap.add_argument("--sizes", default="small,medium,large", help="with --design: which of small, medium, large")
     ap.add_argument("--gemm-compare", type=int, default=0, metavar="TOKENS",
                     help="instead of the bench line: the four products of a layer of --model at TOKENS tokens, this "
@@ -940,6 +1171,8 @@ def main() -> int:
     if args.design:
         if args.context == 8192:
             args.context = 2048
+        if args.design == "fidepel":
+            return fidepel_compare(args, torch)
         return lofirax_compare(args, torch) if args.design == "lofirax" else design_compare(args, torch)
     if args.gemm_compare:
         return gemm_compare(MODELS[args.model], torch, args.gemm_compare, peaks()[1])

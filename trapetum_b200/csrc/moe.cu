@@ -152,16 +152,42 @@ __device__ __forceinline__ void mv_dot(const T* __restrict__ w0, long long ld, i
     constexpr int VEC = 16 / sizeof(T);
 #pragma unroll
     for (int r = 0; r < MV_ROWS; r++) acc[r] = 0.f;
-    if ((K % VEC) == 0 && ((((uintptr_t)w0) | ((uintptr_t)(ld * sizeof(T)))) & 15) == 0) {
-        for (int c = lane * VEC; c < K; c += 32 * VEC) {
-            uint4 wv[MV_ROWS];
+    if ((K % VEC) == 0 && ((((uintptr_t)w0) | ((uintptr_t)(ld * sizeof(T))) | (uintptr_t)__cvta_generic_to_shared(x_s)) & 15) == 0) {
+        // two steps of the row at once: 2 x MV_ROWS loads of 16 bytes are asked for before the first is used
+        for (int c = lane * VEC; c < K; c += 64 * VEC) {
+            const int c2 = c + 32 * VEC;
+            const bool second = c2 < K;
+            uint4 wv[MV_ROWS], wv2[MV_ROWS];
 #pragma unroll
-            for (int r = 0; r < MV_ROWS; r++) wv[r] = r < n_rows ? *(const uint4*)(w0 + (size_t)r * ld + c) : make_uint4(0, 0, 0, 0);
+            for (int r = 0; r < MV_ROWS; r++) wv[r] = r < n_rows ? __ldg((const uint4*)(w0 + (size_t)r * ld + c)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int r = 0; r < MV_ROWS; r++) wv2[r] = (second && r < n_rows) ? __ldg((const uint4*)(w0 + (size_t)r * ld + c2)) : make_uint4(0, 0, 0, 0);
+            // the vector's numbers by 16-byte reads (x_s is 16-byte aligned and K a multiple of VEC): read one by one,
+            // a warp's lanes, VEC numbers apart, meet the same bank VEC times
+            float xv[VEC];
+#pragma unroll
+            for (int k = 0; k < VEC; k += 4) {
+                const float4 q = *(const float4*)(x_s + c + k);
+                xv[k] = q.x; xv[k + 1] = q.y; xv[k + 2] = q.z; xv[k + 3] = q.w;
+            }
 #pragma unroll
             for (int r = 0; r < MV_ROWS; r++) {
                 const T* e = (const T*)&wv[r];
 #pragma unroll
-                for (int k = 0; k < VEC; k++) acc[r] = fmaf(to_f<T>(e[k]), x_s[c + k], acc[r]);
+                for (int k = 0; k < VEC; k++) acc[r] = fmaf(to_f<T>(e[k]), xv[k], acc[r]);
+            }
+            if (second) {
+#pragma unroll
+                for (int k = 0; k < VEC; k += 4) {
+                    const float4 q = *(const float4*)(x_s + c2 + k);
+                    xv[k] = q.x; xv[k + 1] = q.y; xv[k + 2] = q.z; xv[k + 3] = q.w;
+                }
+#pragma unroll
+                for (int r = 0; r < MV_ROWS; r++) {
+                    const T* e = (const T*)&wv2[r];
+#pragma unroll
+                    for (int k = 0; k < VEC; k++) acc[r] = fmaf(to_f<T>(e[k]), xv[k], acc[r]);
+                }
             }
         }
     } else {
@@ -176,7 +202,7 @@ __device__ __forceinline__ void mv_dot(const T* __restrict__ w0, long long ld, i
 template <typename T>
 __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float x_s[];              // [W]
+    extern __shared__ __align__(16) float x_s[];              // [W]
     const int pair = blockIdx.x, t = pair / a.top;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     pdl_wait();
@@ -204,7 +230,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
 template <typename T>
 __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float a_s[];              // [top][ff]
+    extern __shared__ __align__(16) float a_s[];              // [top][ff]
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     pdl_wait();

@@ -57,6 +57,7 @@ class RoutedExperts(FeedForward):
                 or self.keep * (self.E // self.groups) < self.top:
             raise ValueError(f"routed_experts: experts={self.E} top={self.top} groups={self.groups} keep={self.keep}")
         self.shared = None
+        self._ones = []
         self.shared_gate_name = None
         sh = p.get("shared")
         if sh and self.gated:
@@ -122,9 +123,11 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             shared = self.shared.forward(x, ctx)              # float32 partial sums [splits, T, hidden]
             if gate is None:
-                gate = ctx.memo.get("ones")
-                if gate is None or gate.numel() < x.shape[0]:
-                    gate = ctx.memo["ones"] = torch.ones(x.shape[0], dtype=torch.float32, device=x.device)
+                # the shared expert is added as it is: a gate of ones, made once and kept (no launch in a step); a
+                # smaller one that a captured step may still read stays alive beside its successor
+                if not self._ones or self._ones[-1].numel() < x.shape[0]:
+                    self._ones.append(torch.ones(max(256, 2 * x.shape[0]), dtype=torch.float32, device=x.device))
+                gate = self._ones[-1]
         return ops.moe_experts(x, self.w_gate, self.w_up, self.w_down, idx, weight, shared, gate, self.w_gate_up)
 
 
