@@ -16,7 +16,7 @@ import numpy as np
 
 # ``max_tokens`` counts the tokens that live requests hold, not the empty rows of each request's last page:
 # room for that padding of up to this many live requests is added.
-PADDING_PAGES = 16
+PADDING_PAGES = 64
 MAX_LIVE = 256          # slots; a per-sequence state of a recurrent mixer is kept for each
 
 
