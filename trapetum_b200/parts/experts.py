@@ -32,6 +32,9 @@ from .linear import kernel_files as linear_kernels
 from .linear import linear_partials
 
 
+FUSED_UP_TOKENS = 128     # up to here a product comes as split-K partial sums anyway (the swapped tensor-core form)
+
+
 class RoutedExperts(FeedForward):
     graph_safe = True          # the routing stays on the device: no launch depends on which experts were chosen
 
@@ -111,17 +114,29 @@ class RoutedExperts(FeedForward):
         n = self.E + int(self.has_gate)
         rows.append(torch.zeros((-n % 16, self.hidden), dtype=router.dtype, device=router.device))
         self.w_router = torch.cat(rows, dim=0).contiguous()
+        # an ungated shared expert: its up rows lie right behind the router's, so that a step of few tokens makes the
+        # logits and the shared expert's first product with ONE product (both are read as 32-bit partial sums there);
+        # the router and the shared expert keep views of their rows, nothing is stored twice
+        self.w_router_up = None
+        if isinstance(self.shared, PlainMLP) and self.shared.w_up.dtype == self.w_router.dtype:
+            n = self.w_router.shape[0]
+            self.w_router_up = torch.cat([self.w_router, self.shared.w_up], dim=0).contiguous()
+            self.w_router = self.w_router_up[:n]
+            self.shared.w_up = self.w_router_up[n:]
 
     def kernel_files(self):
         return linear_kernels(self.rt.dtype) + ("moe", "activation")
 
     def forward(self, x, ctx):
-        logits = linear_partials(x, self.w_router)             # 32-bit sums; the routing itself is 32-bit throughout
+        fused_up = self.w_router_up is not None and x.shape[0] <= FUSED_UP_TOKENS
+        # 32-bit sums; the routing itself is 32-bit throughout
+        logits = linear_partials(x, self.w_router_up if fused_up else self.w_router)
         idx, weight, gate = ops.moe_route(logits, self.E, self.correction, self.has_gate, self.top, self.groups,
                                           self.keep, self.group_top, self.weight_eps, self.score, self.route_scale)
         shared = None
         if self.shared is not None:
-            shared = self.shared.forward(x, ctx)              # float32 partial sums [splits, T, hidden]
+            # float32 partial sums [splits, T, hidden]
+            shared = self.shared.finish(logits, self.w_router.shape[0]) if fused_up else self.shared.forward(x, ctx)
             if gate is None:
                 # the shared expert is added as it is: a gate of ones, made once and kept (no launch in a step); a
                 # smaller one that a captured step may still read stays alive beside its successor

@@ -112,6 +112,12 @@ class PlainMLP(FeedForward):
             act = ops.unary_act(linear_partials(x, self.w_up), self.activation, self.rt.dtype)
         return linear_partials(act, self.w_down)
 
+    def finish(self, part: torch.Tensor, col0: int) -> torch.Tensor:
+        """The rest of the part when its first product was made together with another one: ``part`` holds
+        ``up(x)`` as 32-bit partial sums in the columns from ``col0`` on."""
+        act = ops.unary_act(part, self.activation, self.rt.dtype, col0, self.inter)
+        return linear_partials(act, self.w_down)
+
 
 class NoFeedForward(FeedForward):
     """A layer without a feed-forward: arrangements that allow it look at ``absent`` and skip the branch."""
