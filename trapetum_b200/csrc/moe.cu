@@ -142,6 +142,22 @@ struct MoeExpertArgs {
     int ungated;                               // experts are D relu(U x)^2: there is no gate matrix
 };
 
+// n numbers of the activations' dtype into shared memory as 32-bit, times `scale`, by all threads of the block: 16 bytes
+// a load where the dtype is 16-bit, n a multiple of 8 and the source 16-byte aligned.
+template <typename T>
+__device__ __forceinline__ void fill_f32(float* __restrict__ dst, const T* __restrict__ src, int n, float scale) {
+    if (sizeof(T) == 2 && (n & 7) == 0 && (((uintptr_t)src) & 15) == 0) {
+        for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+            const uint4 v = *(const uint4*)(src + i);
+            const T* e = (const T*)&v;
+            *(float4*)(dst + i) = make_float4(to_f<T>(e[0]) * scale, to_f<T>(e[1]) * scale, to_f<T>(e[2]) * scale, to_f<T>(e[3]) * scale);
+            *(float4*)(dst + i + 4) = make_float4(to_f<T>(e[4]) * scale, to_f<T>(e[5]) * scale, to_f<T>(e[6]) * scale, to_f<T>(e[7]) * scale);
+        }
+    } else {
+        for (int i = threadIdx.x; i < n; i += blockDim.x) dst[i] = to_f<T>(src[i]) * scale;
+    }
+}
+
 // 16 bytes of a weight row per lane and load where the row allows it; MV_ROWS rows (and for gate/up both matrices) are on
 // their way together, so that a warp keeps enough bytes in flight to stream an expert's matrices at the memory's speed.
 constexpr int MV_ROWS = 4;
@@ -208,7 +224,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(MoeExpertArgs a) {
     pdl_wait();
     const int e = a.idx[pair];
     const T* x = (const T*)a.x + (size_t)t * a.x_stride;
-    for (int c = threadIdx.x; c < a.W; c += blockDim.x) x_s[c] = to_f<T>(x[c]);
+    fill_f32<T>(x_s, x, a.W, 1.f);
     __syncthreads();
     const T* gw = (const T*)a.gate_w + (size_t)e * a.ff * a.W;
     const T* uw = (const T*)a.up_w + (size_t)e * a.ff * a.W;
@@ -234,8 +250,8 @@ __global__ void __launch_bounds__(256) moe_down_kernel(MoeExpertArgs a) {
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarp = blockDim.x >> 5;
     pdl_wait();
-    for (int i = threadIdx.x; i < a.top * a.ff; i += blockDim.x)
-        a_s[i] = to_f<T>(((const T*)a.act)[(size_t)t * a.top * a.ff + i]) * a.weight[(size_t)t * a.top + i / a.ff];
+    for (int k = 0; k < a.top; k++)
+        fill_f32<T>(a_s + (size_t)k * a.ff, (const T*)a.act + ((size_t)t * a.top + k) * a.ff, a.ff, a.weight[(size_t)t * a.top + k]);
     __syncthreads();
     for (int c0 = (blockIdx.y * nwarp + warp) * MV_ROWS; c0 < a.W; c0 += gridDim.y * nwarp * MV_ROWS) {
         const int nr = min(MV_ROWS, a.W - c0);
@@ -625,13 +641,30 @@ extern "C" int tb_moe_route(const MoeRouteArgs* args, cudaStream_t stream) {
     return tb_launch_status();
 }
 
+static int moe_sm_count() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms = n > 0 ? n : 148;
+    }
+    return sms;
+}
+
 extern "C" int tb_moe_gate_up(const MoeExpertArgs* args, int dtype, cudaStream_t stream) {
     const MoeExpertArgs& a = *args;
     if (a.n_tokens <= 0) return 0;
     if (a.W <= 0 || a.W > 12288 || a.ff <= 0 || a.top <= 0) return tb_refuse("moe: W=%d ff=%d top=%d", a.W, a.ff, a.top);
     const int per = 8 * MV_ROWS;                       // rows a CTA's eight warps take in one round
-    const int ys = (a.ff + per - 1) / per < 64 ? (a.ff + per - 1) / per : 64;
-    TB_DISPATCH_1(dtype, T, tb_launch(moe_gate_up_kernel<T>, dim3(a.n_tokens * a.top, ys), dim3(256), (size_t)a.W * sizeof(float), stream, a));
+    // as many CTAs as the device holds at once (four of these an SM), each warp taking the same number of rounds: a
+    // CTA's start (the pair's expert, the token's row into shared memory) is then paid once for several rounds, and
+    // no second, partly filled wave of CTAs follows the first
+    const int pairs = a.n_tokens * a.top, most = (a.ff + per - 1) / per, room = 4 * moe_sm_count();
+    const int rounds = ((long long)pairs * most + room - 1) / room;
+    int ys = (most + rounds - 1) / rounds;
+    if (ys > 64) ys = 64;
+    TB_DISPATCH_1(dtype, T, tb_launch(moe_gate_up_kernel<T>, dim3(pairs, ys), dim3(256), (size_t)a.W * sizeof(float), stream, a));
     return tb_launch_status();
 }
 
