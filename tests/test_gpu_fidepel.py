@@ -221,6 +221,49 @@ def test_the_shared_expert_as_a_part(T, W, ff, dtype):
     near(out.double().sum(0) if out.dim() == 3 else out, plain.expert(x.double(), up.double(), down.double(), rnd), dtype, "down(relu(up x)^2)")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("W, E, top, ff, sff, groups", [(64, 8, 2, 32, 48, (4, 2)), (72, 6, 3, 16, 40, None), (128, 16, 4, 64, 128, (2, 1))])
+def test_router_and_shared_expert_from_one_product_or_two(W, E, top, ff, sff, groups, dtype):
+    """Few tokens take the router's logits and the shared expert's first product from one product over the rows of
+    both, many tokens from two: both agree with the plain implementation, token by token."""
+    from trapetum_b200.parts.base import Runtime, build_part
+    from trapetum_b200.config.base import PartSpec
+    from trapetum_b200.csrc import build
+    from trapetum_b200.parts import experts as experts_part
+    dt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(W + E)
+    mlp = moe(E, top, ff, scale=1.5, groups=groups, shared=sff)
+    t = {"f.router": torch.randn(E, W, generator=g) * 0.5,
+         "f.shared.up": torch.randn(sff, W, generator=g) / 6, "f.shared.down": torch.randn(W, sff, generator=g) / 6}
+    for e in range(E):
+        t[f"f.e{e}.up"], t[f"f.e{e}.down"] = torch.randn(ff, W, generator=g) / 6, torch.randn(W, ff, generator=g) / 6
+    t = {k: v.to(dt) for k, v in t.items()}
+    part = build_part("feed_forward", PartSpec("routed_experts", {
+        "hidden_size": W, "experts": E, "top": top, "intermediate_size": ff, "gated": False, "activation": "relu2",
+        "score": "softmax", "route_scale": 1.5, "groups": groups[0] if groups else 1, "keep_groups": groups[1] if groups else 1,
+        "group_score_of": 1, "weight_eps": 1e-20, "router": "router", "correction": None, "expert": "e{}.", "up": "up",
+        "down": "down", "shared": {"intermediate_size": sff, "up": "shared.up", "down": "shared.down"}}), "f.", Runtime(dt, torch.device(DEV)))
+    build.require(part.kernel_files())
+    part.bind({k: dev(v) for k, v in t.items()})
+    assert part.w_router_up is not None and part.shared.w_up.data_ptr() == part.w_router_up[part.w_router.shape[0]:].data_ptr()
+    rnd = plain.to_bf16 if dtype == "bfloat16" else plain.same
+    td = {k: v.double() for k, v in t.items()}
+
+    class Ctx:
+        memo = {}
+    for T in (3, experts_part.FUSED_UP_TOKENS, experts_part.FUSED_UP_TOKENS + 70):
+        x = torch.randn(T, W, generator=g).to(dt)
+        out = part.forward(dev(x), Ctx())
+        got = (out.double().sum(0) if out.dim() == 3 else out.double()).cpu()
+        want = plain.moe(x.double(), mlp, td, "f.", rnd)
+        plain.MARGINS = []
+        plain.route(x.double(), mlp["router"], td, "f.")
+        sure = plain.MARGINS[0] > (1e-4 if dtype == "float32" else 0.05)      # a rounded product may turn a close call
+        plain.MARGINS = None
+        assert int(sure.sum()) >= T // 2
+        near(got[sure], want[sure], dtype, f"experts with a shared expert, {T} tokens", rel16=2e-2)
+
+
 @pytest.mark.parametrize("T, N, K", [(256, 128, 128), (300, 96, 72)])
 def test_the_tensor_core_product_squares_what_relu_lets_through(T, N, K):
     from trapetum_b200.csrc import ops

@@ -81,7 +81,9 @@ def test_replay_three_ways(model_folders, plain_models, tolerance_of, tmp_path, 
 
 
 def test_replay_refuses_what_does_not_fit(model_folders, tmp_path):
-    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [i % 200 for i in range(2000)], "want": []}], "end": []}]
+    from trapetum_b200.engine.replay import PADDING_PAGES
+    n = 64 + (PADDING_PAGES + 8) * 64          # more than the 64 tokens asked for and the room added for last pages
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": [i % 200 for i in range(n)], "want": []}], "end": []}]
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folders["A"],
                            "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
                           input=json.dumps(steps[0]) + "\n", capture_output=True, text=True, timeout=600)
