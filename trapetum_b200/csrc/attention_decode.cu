@@ -34,6 +34,13 @@ __device__ int g_attn_error = 0;          // 0, or: 1 a bounded wait ran out, 2 
 
 #include "decode_args.h"
 
+// The first key position that the query of a sequence of `len` keys sees (DecodeArgs.window).
+__device__ __forceinline__ int tb_first_key(int window, int len) {
+    if (window > 0) return len > window ? len - window : 0;
+    if (window < 0) return ((len - 1) / (-window)) * (-window);
+    return 0;
+}
+
 template <int HD> struct DCfg {
     static constexpr int NWARP = HD >= 64 ? 16 : 8;                  // more warps hide more latency; a warp needs
     static constexpr int KPW = PAGE / NWARP;                         // at least one pass of 256 / HD keys per page
@@ -75,7 +82,7 @@ __global__ void __launch_bounds__(DCfg<HD>::NWARP * 32, 1) attn_decode_kernel(De
     const int sub = lane % LPK, kg = lane / LPK;
 
     const int len = a.len_after[b];
-    const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+    const int lo = tb_first_key(a.window, len);
     // the rows of this sequence in "row space": positions, or ring rows
     int first_page, n_pages;
     if (a.ring_rows > 0) { first_page = 0; n_pages = (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
@@ -453,7 +460,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     // geometry of a sequence: its pages that hold keys, in row space (positions, or ring rows)
     auto seq_pages = [&](int b, int& first_page, int& hot) -> int {
         const int len = a.len_after[b];
-        const int lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+        const int lo = tb_first_key(a.window, len);
         hot = ((a.ring_rows > 0) ? (len - 1) % a.ring_rows : (len - 1)) / PAGE;
         if (a.ring_rows > 0) { first_page = 0; return (min(len, a.ring_rows) + PAGE - 1) / PAGE; }
         first_page = lo / PAGE;
@@ -718,7 +725,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     bool wrapped = false, no_invalid = false;
     auto set_geometry = [&](int b) {
         len = a.len_after[b];
-        lo = (a.window > 0 && len > a.window) ? len - a.window : 0;
+        lo = tb_first_key(a.window, len);
         wrapped = a.ring_rows > 0 && len >= a.ring_rows;
         const int newest = wrapped ? (len - 1) % a.ring_rows : 0;
         n_old = wrapped ? a.ring_rows - a.window : 0;

@@ -8,7 +8,8 @@
 //
 //   tb_latent_rows     from the 32-bit partial sums of the down projection: c = rms-normed first C columns
 //                      times a weight, r = the last R columns rotated at the token's position (rotate-half
-//                      pairing over the first rot_dims of them); the row goes to the paged cache and to a
+//                      pairing over the first rot_dims of them), times rot_scale; the row goes to the paged cache
+//                      (a ring of ring_rows rows per sequence if that is set) and to a
 //                      packed matrix; all arithmetic 32-bit, the row rounded once
 //   tb_head_linear     y[t, h, :] = W[h] x[t, h, :] for per-head matrices W [heads][out][in]
 //   tb_latent_decode   one query per sequence and head against the cached rows, the key range cut into
@@ -27,6 +28,15 @@ struct LatentRowsArgs {
     const int* page_table; int pt_stride; int page_rows;
     void* pool;                                                // [pages][page_rows][C + R]
     void* rows;                                                // [T][C + R]
+    int ring_rows; const int* len_after;                       // ring_rows > 0: row = position mod ring_rows, and only the
+                                                               // last ring_rows tokens of a sequence ([batch] lengths) are cached
+    float rot_scale;                                           // the rotated part comes times this
+    long long row_stride;                                      // numbers between two tokens' rows of dkv (0: C + R)
+    // the same product may carry, behind the C + R columns, a latent of the queries (Q columns, RMS-normed times
+    // q_norm_w with the same eps, written to cq_out [T][Q] in the output's dtype) and n_gate gate columns (their
+    // sigmoid goes to gate_out [T][n_gate], 32-bit)
+    int Q; const float* q_norm_w; void* cq_out;
+    int n_gate; float* gate_out;
 };
 
 template <typename T>
@@ -34,11 +44,12 @@ __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
     pdl_launch_dependents();
     extern __shared__ float row_s[];
     __shared__ float red[33];
-    const int t = blockIdx.x, W = a.C + a.R;
+    const int t = blockIdx.x, W = a.C + a.R, WA = W + a.Q + a.n_gate;
+    const size_t rs = a.row_stride > 0 ? (size_t)a.row_stride : (size_t)W;
     pdl_wait();
-    float sq = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float* src = a.dkv + (size_t)t * W + c;
+    float sq = 0.f, sq_q = 0.f;
+    for (int c = threadIdx.x; c < WA; c += blockDim.x) {
+        const float* src = a.dkv + (size_t)t * rs + c;
         float v = 0.f;
         int s = 0;
         for (; s + 4 <= a.splits; s += 4) {            // four loads on their way at a time, added in split order
@@ -49,11 +60,22 @@ __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
         for (; s < a.splits; s++) v += src[(size_t)s * a.split_stride];
         row_s[c] = v;
         if (c < a.C) sq = fmaf(v, v, sq);
+        else if (c >= W && c < W + a.Q) sq_q = fmaf(v, v, sq_q);
     }
     const float rinv = 1.f / sqrtf(block_sum(sq, red) / (float)a.C + a.eps);     // its barriers also publish row_s
+    if (a.Q > 0) {
+        const float qinv = 1.f / sqrtf(block_sum(sq_q, red) / (float)a.Q + a.eps);
+        T* cq = (T*)a.cq_out + (size_t)t * a.Q;
+        for (int c = threadIdx.x; c < a.Q; c += blockDim.x) cq[c] = from_f<T>(row_s[W + c] * qinv * a.q_norm_w[c]);
+    }
+    for (int c = threadIdx.x; c < a.n_gate; c += blockDim.x)
+        a.gate_out[(size_t)t * a.n_gate + c] = 1.f / (1.f + expf(-row_s[W + a.Q + c]));
     const int pos = a.positions[t];
-    const int page = a.page_table[(size_t)a.token_seq[t] * a.pt_stride + pos / a.page_rows];
-    T* cache = (T*)a.pool + ((size_t)page * a.page_rows + pos % a.page_rows) * W;
+    const int b = a.token_seq[t];
+    const int crow = a.ring_rows > 0 ? pos % a.ring_rows : pos;
+    const bool keep = a.ring_rows <= 0 || pos >= a.len_after[b] - a.ring_rows;
+    const int page = keep ? a.page_table[(size_t)b * a.pt_stride + crow / a.page_rows] : 0;
+    T* cache = (T*)a.pool + ((size_t)page * a.page_rows + crow % a.page_rows) * W;
     T* out = (T*)a.rows + (size_t)t * W;
     const int half = a.rot_dims / 2;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
@@ -64,16 +86,17 @@ __global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
             const int i = c - a.C;
             if (i < half) {
                 float sn, cs; sincosf((float)pos * a.inv_freq[i], &sn, &cs);
-                v = row_s[c] * cs - row_s[c + half] * sn;
+                v = (row_s[c] * cs - row_s[c + half] * sn) * a.rot_scale;
             } else if (i < 2 * half) {
                 float sn, cs; sincosf((float)pos * a.inv_freq[i - half], &sn, &cs);
-                v = row_s[c] * cs + row_s[c - half] * sn;
+                v = (row_s[c] * cs + row_s[c - half] * sn) * a.rot_scale;
             } else {
                 v = row_s[c];
             }
         }
         const T r = from_f<T>(v);
-        cache[c] = r; out[c] = r;
+        if (keep) cache[c] = r;
+        out[c] = r;
     }
 }
 
@@ -160,7 +183,12 @@ extern "C" int tb_latent_rows(const LatentRowsArgs* args, int dtype, cudaStream_
     if (a.n_tokens <= 0) return 0;
     if (a.C <= 0 || a.R < 0 || a.rot_dims < 0 || a.rot_dims % 2 || a.rot_dims > a.R || a.page_rows <= 0)
         return tb_refuse("latent_rows: C=%d R=%d rot_dims=%d page_rows=%d", a.C, a.R, a.rot_dims, a.page_rows);
-    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(128), (size_t)(a.C + a.R) * sizeof(float), stream, a));
+    if (a.Q < 0 || a.n_gate < 0 || (a.Q > 0 && (a.q_norm_w == nullptr || a.cq_out == nullptr)) || (a.n_gate > 0 && a.gate_out == nullptr))
+        return tb_refuse("latent_rows: Q=%d gate=%d need their outputs", a.Q, a.n_gate);
+    if (a.ring_rows > 0 && (a.ring_rows % a.page_rows || a.len_after == nullptr))
+        return tb_refuse("latent_rows: a ring of %d rows needs whole pages and the sequences' lengths", a.ring_rows);
+    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(128),
+                                      (size_t)(a.C + a.R + a.Q + a.n_gate) * sizeof(float), stream, a));
     return tb_launch_status();
 }
 
@@ -175,7 +203,11 @@ struct LatentDecodeArgs {
     float* partial;                                    // [batch][heads][splits][C + 2] when splits > 1
     int heads, C, R, out_dim, n_splits;
     float scale;
+    int window;                                        // 0: every earlier row; W: the last W rows, the query's own included
+    int ring_rows;                                     // 0: row = position; else row = position mod ring_rows
 };
+
+__device__ __forceinline__ int latent_first_key(int window, int len) { return (window > 0 && len > window) ? len - window : 0; }
 
 template <int NC>
 struct LatAcc {
@@ -199,24 +231,27 @@ __global__ void __launch_bounds__(128) latent_decode_kernel(LatentDecodeArgs a) 
     for (int e = threadIdx.x; e < KD; e += blockDim.x) q_s[e] = to_f<T>(qrow[e]);
     __syncthreads();
     const int len = a.len_after[b];
-    int per = (len + a.n_splits - 1) / a.n_splits;
+    const int lo = latent_first_key(a.window, len), lo32 = lo & ~31;
+    int per = (len - lo32 + a.n_splits - 1) / a.n_splits;
     per = (per + 31) & ~31;
-    const int beg = split * per, end = min(len, beg + per);
+    const int beg = lo32 + split * per, end = min(len, beg + per);
     const int* pt = a.page_table + (size_t)b * a.pt_stride;
 
     LatAcc<NC> acc; acc.init();
     for (int j0 = beg + warp * 32; j0 < end; j0 += nwarp * 32) {
         const int j = j0 + lane;
-        const bool valid = j < end;
+        const bool valid = j < end && j >= lo;
         const T* krow = nullptr;
         float s = -INFINITY;
         if (valid) {
-            krow = (const T*)a.pool + ((size_t)pt[j / a.page_rows] * a.page_rows + (j % a.page_rows)) * KD;
+            const int r = a.ring_rows > 0 ? j % a.ring_rows : j;
+            krow = (const T*)a.pool + ((size_t)pt[r / a.page_rows] * a.page_rows + (r % a.page_rows)) * KD;
             float d = 0.f;
             for (int e = 0; e < KD; e++) d = fmaf(q_s[e], to_f<T>(krow[e]), d);
             s = d * a.scale;
         }
         const float cm = warp_max(s);
+        if (cm == -INFINITY) continue;                 // 32 rows before the window's first
         const float m_new = fmaxf(acc.m, cm);
         const float corr = (acc.m == -INFINITY) ? 0.f : expf(acc.m - m_new);
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -358,18 +393,20 @@ __global__ void __launch_bounds__(MT * 128) latent_decode_mma_kernel(LatentDecod
     const int h0 = hg * HEADS, nh = min(HEADS, a.heads - h0);
     pdl_wait();
     const int len = a.len_after[b];
-    int per = (len + a.n_splits - 1) / a.n_splits;
+    const int lo = latent_first_key(a.window, len), lo32 = lo / LD_BN * LD_BN;
+    int per = (len - lo32 + a.n_splits - 1) / a.n_splits;
     per = (per + LD_BN - 1) / LD_BN * LD_BN;
-    const int beg = split * per, end = min(len, beg + per);
+    const int beg = lo32 + split * per, end = min(len, beg + per);
     const int* pt = a.page_table + (size_t)b * a.pt_stride;
     const bf16* pool = (const bf16*)a.pool;
     const int chunks = KD / 8;                                      // 16-byte pieces of a row
     auto load = [&](int stage, int j0) {
-        const bf16* src = pool + ((size_t)pt[j0 / a.page_rows] * a.page_rows + (j0 % a.page_rows)) * KD;
+        const int r0 = a.ring_rows > 0 ? j0 % a.ring_rows : j0;       // 32 rows that start at a multiple of 32 lie in one page
+        const bf16* src = pool + ((size_t)pt[r0 / a.page_rows] * a.page_rows + (r0 % a.page_rows)) * KD;
         unsigned char* dst = k_s + (size_t)stage * LD_BN * pitch;
         for (int c = threadIdx.x; c < LD_BN * chunks; c += THREADS) {
             const int r = c / chunks, ch = c % chunks;
-            ld_cp16(dst + r * pitch + ch * 16, src + (size_t)r * KD + ch * 8, j0 + r < end);
+            ld_cp16(dst + r * pitch + ch * 16, src + (size_t)r * KD + ch * 8, j0 + r < end && j0 + r >= lo);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -429,7 +466,7 @@ __global__ void __launch_bounds__(MT * 128) latent_decode_mma_kernel(LatentDecod
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int r = warp * 4 + i;
-            const float v = (j0 + lane < end) ? s_s[r * LD_BN + lane] : -INFINITY;
+            const float v = (j0 + lane < end && j0 + lane >= lo) ? s_s[r * LD_BN + lane] : -INFINITY;
             const float mn = fmaxf(m_run[i], warp_max(v));
             const float corr = (m_run[i] == -INFINITY) ? 0.f : expf(m_run[i] - mn);
             const float p = (v == -INFINITY) ? 0.f : expf(v - mn);

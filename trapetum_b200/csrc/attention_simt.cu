@@ -5,7 +5,8 @@
 // Per query i and key j of the same sequence (runtime/cuda/codebook_gemv.cu:240-270
 // is the reference's one-query form):
 //   s = (q_i . k_j) * scale;  if cap: s = cap*tanh(s/cap);
-//   visible(i, j) = j <= i and (window == 0 or i - j < window);
+//   visible(i, j) = j <= i and (window == 0 or i - j < window); a negative window -c stands for blocks of c
+//                   positions counted from position 0: j <= i and floor(i / c) == floor(j / c);
 //   p = softmax over visible j (running max subtracted);  o_i = sum_j p_ij v_j
 // with query head h reading kv head h / (n_heads / n_kv_heads).  Dot products,
 // cap, softmax and the weighted sum are 32-bit.  The reference takes
@@ -23,8 +24,14 @@
 
 TB_EXPORT_ERROR()
 
+// The first position that a query at position i sees.
+__device__ __forceinline__ int first_visible(int i, int window) {
+    if (window > 0) return i - window + 1 > 0 ? i - window + 1 : 0;
+    if (window < 0) return (i / (-window)) * (-window);
+    return 0;
+}
 __device__ __forceinline__ bool visible(int i, int j, int window) {
-    return j <= i && (window <= 0 || i - j < window);
+    return j <= i && j >= first_visible(i, window);
 }
 
 // Running softmax state of one warp for one (query, head).
@@ -99,7 +106,7 @@ __global__ void attn_prefill_simt_kernel(const T* __restrict__ q, const T* __res
     __syncwarp();
 
     WarpAcc<NC> acc; acc.init();
-    const int lo = (window > 0 && i - window + 1 > 0) ? i - window + 1 : 0;
+    const int lo = first_visible(i, window);
     for (int j0 = lo; j0 <= i; j0 += 32) {
         const int j = j0 + lane;
         const bool valid = visible(i, j, window);
@@ -144,7 +151,7 @@ __global__ void attn_decode_simt_kernel(DecodeArgs a) {
 
     const int len = a.len_after[b];
     const int i = len - 1;                                  // the query's position
-    const int lo = (a.window > 0 && len - a.window > 0) ? len - a.window : 0;
+    const int lo = first_visible(i, a.window);
     int per = (len - lo + a.n_splits - 1) / a.n_splits;
     per = (per + 31) & ~31;
     const int beg = lo + split * per;
@@ -286,8 +293,8 @@ extern "C" int tb_attn_decode_simt(const DecodeArgs* args, int dtype, int batch,
     if (a.n_splits > 1 && a.partial == nullptr) return tb_refuse("attention: splits need scratch");
     if (a.page_rows <= 0 || (a.ring_rows > 0 && a.ring_rows % a.page_rows))
         return tb_refuse("attention: page_rows=%d ring_rows=%d", a.page_rows, a.ring_rows);
-    if (a.ring_rows > 0 && (a.window <= 0 || a.window > a.ring_rows))
-        return tb_refuse("attention: a ring of %d rows cannot hold a window of %d", a.ring_rows, a.window);
+    if (a.ring_rows > 0 && (a.window == 0 || abs(a.window) > a.ring_rows))
+        return tb_refuse("attention: a ring of %d rows cannot hold a window of %d", a.ring_rows, abs(a.window));
     const int warps = 4;
     const size_t smem = ((size_t)hd + (size_t)warps * (hd + 2)) * sizeof(float);
     dim3 grid(batch, a.n_heads, a.n_splits);

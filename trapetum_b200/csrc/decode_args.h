@@ -26,7 +26,9 @@ typedef struct DecodeArgs {
                                    (tb_attn_decode_noalloc ignores it and uses its own) */
     int n_heads, n_kv_heads, hd, page_rows;
     int ring_rows;              /* 0: row = position; else the line is a ring, row = position mod ring_rows */
-    int window;                 /* 0: every earlier key is visible; W: the last W keys, the query's own included */
+    int window;                 /* 0: every earlier key is visible; W: the last W keys, the query's own included;
+                                   -C (lines without a ring only): the keys of the query's own block of C positions,
+                                   blocks counted from position 0 */
     int n_splits;               /* pieces each sequence's keys are cut into */
     float scale;                /* scores are (q . k) * scale */
     float cap;                  /* 0: off; else scores become cap * tanh(score / cap) */

@@ -487,7 +487,7 @@ class _ProjNormKvArgs(ctypes.Structure):
                 ("rotary_dim", c_int), ("inv_freq", c_void_p),
                 ("positions", c_void_p), ("token_seq", c_void_p), ("len_after", c_void_p),
                 ("k_pool", c_void_p), ("v_pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
-                ("page_rows", c_int), ("ring_rows", c_int)]
+                ("page_rows", c_int), ("ring_rows", c_int), ("bias", c_void_p)]
 
 
 def projnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, vdim: int, padded: int,
@@ -495,14 +495,16 @@ def projnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, 
                 head_scale: Optional[torch.Tensor], rotary_dim: int, inv_freq: Optional[torch.Tensor], has_gate: bool,
                 positions: torch.Tensor, token_seq: torch.Tensor, len_after: torch.Tensor,
                 k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], page_table: Optional[torch.Tensor],
-                ring_rows: int):
+                ring_rows: int, bias: Optional[torch.Tensor] = None):
     """From the q/k/v(/gate) product's float32 partial sums [splits, T, H dim + G dim + G vdim (+ H)] to
     ([T, (H + 2 G) * padded] in ``out_dtype``, sigmoid of the gate columns float32 [T, H] or None): q and k divided by
     their root mean square over the whole projection times ``q_norm_w`` / ``k_norm_w`` (float32; None: no norm), q heads
     times ``head_scale[h]`` (float32 [H] or None), the first ``rotary_dim`` dims of every q and k head rotated at the
     token's position, every head padded with zeros to ``padded`` numbers; k and v are also written to the cache line
-    (pools [pages, G, PAGE_ROWS, padded])."""
-    _cuda(partial, q_norm_w, k_norm_w, head_scale, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table)
+    (pools [pages, G, PAGE_ROWS, padded]).  ``bias``: float32, one number per column of the product (the width rounded
+    up to a multiple of four), added to the summed row before anything else.  ``n_kv_heads`` 0: the product holds
+    queries only."""
+    _cuda(partial, q_norm_w, k_norm_w, head_scale, inv_freq, positions, token_seq, len_after, k_pool, v_pool, page_table, bias)
     H, G = n_heads, n_kv_heads
     in_width = H * dim + G * (dim + vdim) + (H if has_gate else 0)
     if partial.dtype != torch.float32 or partial.dim() != 3 or partial.stride(2) != 1 or partial.shape[2] < in_width:
@@ -517,6 +519,8 @@ def projnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, 
             raise KernelError(f"projnorm_kv: {name} must be contiguous float32 [{n}]")
     if rotary_dim and inv_freq is None:
         raise KernelError("projnorm_kv: a rotation needs its table")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() < (in_width + 3) // 4 * 4 or not bias.is_contiguous()):
+        raise KernelError(f"projnorm_kv: the bias must be contiguous float32 [>= {(in_width + 3) // 4 * 4}]")
     if k_pool is not None:
         for p in (k_pool, v_pool):
             if p is None or p.dtype != out_dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (G, PAGE_ROWS, padded):
@@ -541,6 +545,7 @@ def projnorm_kv(partial: torch.Tensor, n_heads: int, n_kv_heads: int, dim: int, 
     a.page_table = page_table.data_ptr() if k_pool is not None else None
     a.pt_stride = page_table.stride(0) if k_pool is not None else 0
     a.page_rows = PAGE_ROWS; a.ring_rows = ring_rows
+    a.bias = bias.data_ptr() if bias is not None else None
     lib = build.load("projnorm_kv")
     _check(lib, lib.tb_projnorm_kv(ctypes.byref(a), c_int(code(out_dtype)), c_int(T), _stream()), "projnorm_kv")
     return out, gate
@@ -557,6 +562,21 @@ def head_gate(o: torch.Tensor, gate: torch.Tensor, n_heads: int) -> torch.Tensor
     _check(lib, lib.tb_head_gate(_ptr(o), c_int(code(o.dtype)), _ptr(gate), c_int(T), c_int(n_heads),
                                  c_int(o.shape[1] // n_heads), _stream()), "head_gate")
     return o
+
+
+def head_difference(a: torch.Tensor, n_heads: int, D: int, vdim: int, lam: float, eps: float, out_scale: float) -> torch.Tensor:
+    """An attention output whose heads come in pairs, ``a`` [T, n_heads * 2 * D] (per head: the first map's output,
+    then the second's), folded to [T, n_heads * D]: ``o = a1 - lam * a2`` over the first ``vdim`` numbers of a head,
+    divided by its root mean square (``eps`` inside the root), times ``out_scale``; zeros in the padding.  32-bit."""
+    _cuda(a)
+    T = a.shape[0]
+    if a.dim() != 2 or not a.is_contiguous() or a.shape[1] != n_heads * 2 * D:
+        raise KernelError(f"head_difference: {tuple(a.shape)} is not [T, {n_heads} * 2 * {D}] contiguous")
+    out = torch.empty((T, n_heads * D), dtype=a.dtype, device=a.device)
+    lib = build.load("projnorm_kv")
+    _check(lib, lib.tb_head_difference(_ptr(a), _ptr(out), c_int(code(a.dtype)), c_int(T), c_int(n_heads), c_int(D), c_int(vdim),
+                                       c_float(lam), c_float(eps), c_float(out_scale), _stream()), "head_difference")
+    return out
 
 
 class _Mamba2Args(ctypes.Structure):
@@ -1383,21 +1403,37 @@ class _LatentRowsArgs(ctypes.Structure):
     _fields_ = [("dkv", c_void_p), ("splits", c_int), ("split_stride", c_longlong), ("norm_w", c_void_p), ("eps", c_float),
                 ("inv_freq", c_void_p), ("rot_dims", c_int), ("C", c_int), ("R", c_int), ("n_tokens", c_int),
                 ("positions", c_void_p), ("token_seq", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
-                ("page_rows", c_int), ("pool", c_void_p), ("rows", c_void_p)]
+                ("page_rows", c_int), ("pool", c_void_p), ("rows", c_void_p),
+                ("ring_rows", c_int), ("len_after", c_void_p), ("rot_scale", c_float), ("row_stride", c_longlong),
+                ("Q", c_int), ("q_norm_w", c_void_p), ("cq_out", c_void_p), ("n_gate", c_int), ("gate_out", c_void_p)]
 
 
 def latent_rows(part: torch.Tensor, norm_w: torch.Tensor, eps: float, inv_freq: Optional[torch.Tensor], rot_dims: int,
                 C: int, R: int, positions: torch.Tensor, token_seq: torch.Tensor, pool: torch.Tensor,
-                page_table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+                page_table: torch.Tensor, out_dtype: torch.dtype, ring_rows: int = 0,
+                len_after: Optional[torch.Tensor] = None, rot_scale: float = 1.0,
+                q_norm_w: Optional[torch.Tensor] = None, n_gate: int = 0):
     """From the down projection's partial sums ``part`` float32 [splits, T, C + R] to the cached rows: the first C
     columns RMS-normed times ``norm_w``, the last R rotated at the token's position; written to the paged ``pool``
-    [pages, 1, PAGE_ROWS, C + R] and returned packed [T, C + R], both in ``out_dtype``."""
-    _cuda(part, norm_w, inv_freq, positions, token_seq, pool, page_table)
+    [pages, 1, PAGE_ROWS, C + R] and returned packed [T, C + R], both in ``out_dtype``.  ``ring_rows`` > 0: the cache
+    line is a ring (row = position mod ring_rows; of a sequence with ``len_after`` tokens only the last ring_rows are
+    written).  ``rot_scale``: the rotated columns come times this.  With ``q_norm_w`` (float32 [Q]) and/or ``n_gate`` the
+    product carries more columns behind the C + R: Q numbers that are RMS-normed times ``q_norm_w`` (same eps) and
+    ``n_gate`` numbers whose sigmoid is taken; the result is then (rows, normed [T, Q] in ``out_dtype`` or None,
+    gates float32 [T, n_gate] or None)."""
+    _cuda(part, norm_w, inv_freq, positions, token_seq, pool, page_table, len_after, q_norm_w)
+    more = q_norm_w is not None or n_gate > 0
+    Q = q_norm_w.numel() if q_norm_w is not None else 0
+    if ring_rows and (len_after is None or ring_rows % PAGE_ROWS):
+        raise KernelError("latent_rows: a ring needs the sequences' lengths and whole pages")
     if part.dim() == 2:
         part = part[None]
     T = part.shape[1]
-    if part.dtype != torch.float32 or part.shape[2] != C + R or part.stride(2) != 1 or part.stride(1) != C + R:
-        raise KernelError(f"latent_rows: partial sums must be float32 [splits, T, {C + R}], got {tuple(part.shape)}")
+    if part.dtype != torch.float32 or part.shape[2] < C + R + Q + n_gate or part.stride(2) != 1 \
+            or (not more and (part.shape[2] != C + R or part.stride(1) != C + R)):
+        raise KernelError(f"latent_rows: partial sums must be float32 [splits, T, {C + R + Q + n_gate}], got {tuple(part.shape)}")
+    if q_norm_w is not None and (q_norm_w.dtype != torch.float32 or not q_norm_w.is_contiguous()):
+        raise KernelError("latent_rows: the queries' norm weight must be contiguous float32")
     if norm_w.dtype != torch.float32 or norm_w.numel() != C or not norm_w.is_contiguous():
         raise KernelError(f"latent_rows: the norm weight must be contiguous float32 [{C}]")
     if rot_dims and (inv_freq is None or inv_freq.dtype != torch.float32 or inv_freq.numel() != rot_dims // 2):
@@ -1414,9 +1450,15 @@ def latent_rows(part: torch.Tensor, norm_w: torch.Tensor, eps: float, inv_freq: 
     a.positions = positions.data_ptr(); a.token_seq = token_seq.data_ptr()
     a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0); a.page_rows = PAGE_ROWS
     a.pool = pool.data_ptr(); a.rows = rows.data_ptr()
+    a.ring_rows = ring_rows; a.len_after = len_after.data_ptr() if ring_rows else None; a.rot_scale = rot_scale
+    a.row_stride = part.stride(1)
+    cq = torch.empty((T, Q), dtype=out_dtype, device=part.device) if Q else None
+    gates = torch.empty((T, n_gate), dtype=torch.float32, device=part.device) if n_gate else None
+    a.Q = Q; a.q_norm_w = q_norm_w.data_ptr() if Q else None; a.cq_out = cq.data_ptr() if Q else None
+    a.n_gate = n_gate; a.gate_out = gates.data_ptr() if n_gate else None
     lib = build.load("attention_latent")
     _check(lib, lib.tb_latent_rows(ctypes.byref(a), c_int(code(out_dtype)), _stream()), "latent_rows")
-    return rows
+    return (rows, cq, gates) if more else rows
 
 
 def head_linear(x: torch.Tensor, w: torch.Tensor, heads: int) -> torch.Tensor:
@@ -1439,15 +1481,21 @@ class _LatentDecodeArgs(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("q_stride", c_longlong), ("pool", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
                 ("page_rows", c_int), ("len_after", c_void_p), ("sink", c_void_p), ("out", c_void_p), ("out_stride", c_longlong),
                 ("partial", c_void_p), ("heads", c_int), ("C", c_int), ("R", c_int), ("out_dim", c_int), ("n_splits", c_int),
-                ("scale", c_float)]
+                ("scale", c_float), ("window", c_int), ("ring_rows", c_int)]
 
 
 def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor, len_after: torch.Tensor,
-                  sink: Optional[torch.Tensor], heads: int, C: int, R: int, scale: float, len_bucket: int) -> torch.Tensor:
+                  sink: Optional[torch.Tensor], heads: int, C: int, R: int, scale: float, len_bucket: int,
+                  window: int = 0, ring_rows: int = 0) -> torch.Tensor:
     """One mapped query [heads * (C + R)] per sequence against its cached rows; returns [batch, heads * C] (the weighted
     sums of the rows' first C columns).  ``len_bucket``: an upper bound of the longest context, which the number of
-    pieces a sequence is cut into depends on (and nothing else does, so that a captured step stays valid)."""
+    pieces a sequence is cut into depends on (and nothing else does, so that a captured step stays valid).
+    ``window`` W > 0: only the last W rows are seen; ``ring_rows`` > 0: the line is a ring of that many rows."""
     _cuda(q, pool, page_table, len_after, sink)
+    if ring_rows and (not 0 < window <= ring_rows or ring_rows % PAGE_ROWS):
+        raise KernelError(f"latent_decode: a ring of {ring_rows} rows cannot hold a window of {window}")
+    if window:
+        len_bucket = min(len_bucket, window + 31)
     _rows_contig(q, "latent_decode: q")
     B = q.shape[0]
     if q.shape[1] != heads * (C + R) or pool.dtype != q.dtype:
@@ -1469,6 +1517,7 @@ def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
     a.len_after = len_after.data_ptr(); a.sink = sink.data_ptr() if sink is not None else None
     a.out = out.data_ptr(); a.out_stride = out.stride(0); a.partial = scratch.data_ptr() if scratch is not None else None
     a.heads = heads; a.C = C; a.R = R; a.out_dim = C; a.n_splits = pieces; a.scale = scale
+    a.window = window or 0; a.ring_rows = ring_rows
     if mma:
         _check(lib, lib.tb_latent_decode_mma(ctypes.byref(a), c_int(B), _stream()), "latent_decode_mma", 2)
     else:
@@ -1477,7 +1526,8 @@ def latent_decode(q: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
     return out
 
 
-def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, sink, max_seq_len, seq_lens=None) -> torch.Tensor:
+def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, sink, max_seq_len, seq_lens=None,
+                      window: int = 0) -> torch.Tensor:
     """Causal prefill attention of packed sequences, one kv head per query head, whose softmax denominators also
     hold ``exp(sink[h])`` (``sink`` float32 [n_heads], or None).  bfloat16 runs on the tcgen05 kernel (head sizes 64, 128,
     256, with the sequences' lengths on the host in ``seq_lens``) or the mma.sync kernel (other multiples of 16),
@@ -1498,21 +1548,89 @@ def attn_prefill_sink(q, k, v, seq_start, token_seq, n_heads, head_dim, scale, s
         _check(lib, lib.tb_attn_prefill_tc_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
                                               _ptr(seq_start), _ptr(out), c_int(T), c_int(B), c_int(max(seq_lens)),
                                               c_int(n_heads), c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0),
-                                              c_int(0), _ptr(sink), _stream()), "attn_prefill_tc", 2)
+                                              c_int(window or 0), _ptr(sink), _stream()), "attn_prefill_tc", 2)
         return out
     if attn_prefill_takes(q.dtype, head_dim) and aligned:
         lib = build.load(attn_prefill_lib(head_dim))
         B = seq_start.numel() - 1
         _check(lib, lib.tb_attn_prefill_mma_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
                                                _ptr(seq_start), _ptr(out), c_int(B), c_int(max_seq_len), c_int(n_heads),
-                                               c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0), c_int(0),
+                                               c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0), c_int(window or 0),
                                                _ptr(sink), _stream()), "attn_prefill_mma")
         return out
     lib = build.load("attention_simt")
     _check(lib, lib.tb_attn_prefill_simt_ex(_ptr(q), _ptr(k), _ptr(v), c_longlong(q.stride(0)), c_longlong(k.stride(0)),
                                             _ptr(seq_start), _ptr(token_seq), _ptr(out), c_int(code(q.dtype)), c_int(T),
                                             c_int(n_heads), c_int(n_heads), c_int(head_dim), c_float(scale), c_float(0.0),
-                                            c_int(0), _ptr(sink), _stream()), "attn_prefill_simt")
+                                            c_int(window or 0), _ptr(sink), _stream()), "attn_prefill_simt")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# Attention whose heads' scores are mixed before the softmax
+# ---------------------------------------------------------------------------
+class _MixedAttnArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("q_stride", c_longlong), ("k", c_void_p), ("v", c_void_p), ("kv_stride", c_longlong),
+                ("seq_start", c_void_p), ("token_seq", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
+                ("page_rows", c_int), ("ring_rows", c_int), ("len_after", c_void_p), ("out", c_void_p),
+                ("out_stride", c_longlong), ("mix", c_void_p), ("partial", c_void_p), ("H", c_int), ("G", c_int), ("D", c_int),
+                ("n_tokens", c_int), ("window", c_int), ("unit_sink", c_int), ("n_pieces", c_int)]
+
+
+def _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink):
+    _rows_contig(q, "attn_mixed: q")
+    if q.shape[1] != n_heads * head_dim:
+        raise KernelError(f"attn_mixed: q {tuple(q.shape)} does not hold {n_heads} heads of {head_dim}")
+    if mix.dtype != torch.float32 or tuple(mix.shape) != (n_heads, n_heads) or not mix.is_contiguous():
+        raise KernelError(f"attn_mixed: the mixing matrix must be contiguous float32 [{n_heads}, {n_heads}]")
+    out = torch.empty((q.shape[0], n_heads * head_dim), dtype=q.dtype, device=q.device)
+    a = _MixedAttnArgs()
+    a.q = q.data_ptr(); a.q_stride = q.stride(0); a.out = out.data_ptr(); a.out_stride = out.stride(0)
+    a.mix = mix.data_ptr(); a.H = n_heads; a.G = n_kv_heads; a.D = head_dim; a.n_tokens = q.shape[0]
+    a.window = window or 0; a.unit_sink = int(bool(unit_sink)); a.n_pieces = 1; a.page_rows = PAGE_ROWS
+    return a, out
+
+
+def attn_mixed_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start: torch.Tensor, token_seq: torch.Tensor,
+                       n_heads: int, n_kv_heads: int, head_dim: int, mix: torch.Tensor, window: int,
+                       unit_sink: bool) -> torch.Tensor:
+    """Causal attention of packed sequences whose scores are mixed across heads before the softmax:
+    ``s_h = sum_g mix[h, g] (q_g . k)`` (``mix`` float32 [H, H]; the caller folds the scale in).  ``window`` W > 0: the
+    last W positions are seen; -C: the positions of the query's own block of C, blocks counted from position 0; 0: all
+    earlier ones.  ``unit_sink``: the softmax denominator also holds exp(0)."""
+    _cuda(q, k, v, seq_start, token_seq, mix)
+    for name, t in (("k", k), ("v", v)):
+        _rows_contig(t, "attn_mixed: " + name)
+    if k.stride(0) != v.stride(0) or k.dtype != q.dtype or v.dtype != q.dtype or k.shape[1] != n_kv_heads * head_dim:
+        raise KernelError("attn_mixed: k and v must share row stride and dtype with q and hold the kv heads")
+    a, out = _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink)
+    a.k = k.data_ptr(); a.v = v.data_ptr(); a.kv_stride = k.stride(0)
+    a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr()
+    lib = build.load("attention_mixed")
+    _check(lib, lib.tb_attn_mixed_prefill(ctypes.byref(a), c_int(code(q.dtype)), _stream()), "attn_mixed_prefill")
+    return out
+
+
+def attn_mixed_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
+                      len_after: torch.Tensor, n_heads: int, n_kv_heads: int, head_dim: int, mix: torch.Tensor, window: int,
+                      unit_sink: bool, ring_rows: int, len_bucket: int) -> torch.Tensor:
+    """One query per sequence against the paged cache, scores mixed across heads (see :func:`attn_mixed_prefill`).
+    ``len_bucket``: an upper bound of the longest context, which the number of pieces depends on (and nothing else)."""
+    _cuda(q, k_pool, v_pool, page_table, len_after, mix)
+    for p in (k_pool, v_pool):
+        if p.dtype != q.dtype or not p.is_contiguous() or tuple(p.shape[1:]) != (n_kv_heads, PAGE_ROWS, head_dim):
+            raise KernelError("attn_mixed: cache pools must be contiguous [pages, n_kv_heads, PAGE_ROWS, head_dim] of q's dtype")
+    a, out = _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink)
+    B = q.shape[0]
+    reach = min(len_bucket, abs(window)) if window else len_bucket
+    pieces = max(1, min((reach + 255) // 256, max(1, (2 * sm_count(q.device)) // max(1, B))))
+    scratch = torch.empty(B * n_heads * pieces * (head_dim + 2), dtype=torch.float32, device=q.device) if pieces > 1 else None
+    a.k = k_pool.data_ptr(); a.v = v_pool.data_ptr(); a.page_table = page_table.data_ptr(); a.pt_stride = page_table.stride(0)
+    a.ring_rows = ring_rows; a.len_after = len_after.data_ptr(); a.n_pieces = pieces
+    a.partial = scratch.data_ptr() if scratch is not None else None
+    lib = build.load("attention_mixed")
+    _check(lib, lib.tb_attn_mixed_decode(ctypes.byref(a), c_int(code(q.dtype)), _stream()), "attn_mixed_decode",
+           2 if pieces > 1 else 1)
     return out
 
 

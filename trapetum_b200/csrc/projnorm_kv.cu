@@ -17,7 +17,12 @@
 // ring_rows : pos, page = page_table[seq, row / page_rows]; in a ring only tokens with pos >= len_after - ring_rows
 // are written).
 //
+// A bias (one 32-bit number per column of the product) is added to the summed row first, if given.
+//
 // tb_head_gate multiplies every head of an attention output [tokens][H x D] by its token's gate, in place.
+//
+// tb_head_difference folds an attention output whose heads come in pairs (two score maps over the same values):
+// o = a1 - lam * a2 over the head's first vdim numbers, o / sqrt(mean(o^2) + eps) * out_scale, zeros in the padding.
 //
 // One CTA per token (256 threads, 1,024 when the tokens are few); the token's summed row lies in shared memory.
 #include "common.cuh"
@@ -35,6 +40,7 @@ struct ProjNormKvArgs {
     int rotary_dim; const float* inv_freq;        // [rotary_dim / 2]
     const int* positions; const int* token_seq; const int* len_after;
     void* k_pool; void* v_pool; const int* page_table; int pt_stride; int page_rows; int ring_rows;
+    const float* bias;                            // [in_width rounded up to 4] added to the summed row, or null
 };
 
 // Eight (four) consecutive numbers of an output row, rounded and stored with one or two wide stores.
@@ -95,7 +101,8 @@ __global__ void __launch_bounds__(1024) projnorm_kv_kernel(ProjNormKvArgs a) {
             // a prompt's product comes whole: four pieces of the row in flight per thread
 #pragma unroll 4
             for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-                const float4 r = __ldg(s4 + i);
+                float4 r = __ldg(s4 + i);
+                if (a.bias != nullptr) { const float4 bb = __ldg((const float4*)a.bias + i); r.x += bb.x; r.y += bb.y; r.z += bb.z; r.w += bb.w; }
                 row4[i] = r;
                 const float s2 = r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
                 if (i < q4) ssq += s2; else if (i < k4) ssk += s2;
@@ -109,6 +116,7 @@ __global__ void __launch_bounds__(1024) projnorm_kv_kernel(ProjNormKvArgs a) {
                     const float4 v = __ldg(s4 + sp * st4 + i);
                     r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w;
                 }
+                if (a.bias != nullptr) { const float4 bb = __ldg((const float4*)a.bias + i); r.x += bb.x; r.y += bb.y; r.z += bb.z; r.w += bb.w; }
                 row4[i] = r;
                 const float s2 = r.x * r.x + r.y * r.y + r.z * r.z + r.w * r.w;
                 if (i < q4) ssq += s2; else if (i < k4) ssk += s2;
@@ -118,6 +126,7 @@ __global__ void __launch_bounds__(1024) projnorm_kv_kernel(ProjNormKvArgs a) {
         for (int i = threadIdx.x; i < in_width; i += blockDim.x) {
             float s = 0.f;
             for (int sp = 0; sp < a.n_splits; sp++) s += src[(size_t)sp * a.split_stride + i];       // in split order
+            if (a.bias != nullptr) s += a.bias[i];
             row[i] = s;
             if (i < nq) ssq += s * s; else if (i < nq + nk) ssk += s * s;
         }
@@ -241,7 +250,7 @@ __global__ void __launch_bounds__(1024) projnorm_kv_kernel(ProjNormKvArgs a) {
 extern "C" int tb_projnorm_kv(const ProjNormKvArgs* args, int out_dtype, int n_tokens, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     ProjNormKvArgs a = *args;
-    if (a.n_heads <= 0 || a.n_kv_heads <= 0 || a.dim <= 0 || a.vdim <= 0 || a.D < a.dim || a.D < a.vdim)
+    if (a.n_heads <= 0 || a.n_kv_heads < 0 || a.dim <= 0 || a.vdim <= 0 || a.D < a.dim || a.D < a.vdim)
         return tb_refuse("projnorm_kv: heads=%d kv heads=%d dim=%d vdim=%d padded to %d", a.n_heads, a.n_kv_heads, a.dim, a.vdim, a.D);
     if (a.partial == nullptr || a.n_splits < 1) return tb_refuse("projnorm_kv: needs the product's partial sums");
     if (a.rotary_dim < 0 || a.rotary_dim % 2 || a.rotary_dim > a.dim || (a.rotary_dim > 0 && a.inv_freq == nullptr))
@@ -260,7 +269,8 @@ extern "C" int tb_projnorm_kv(const ProjNormKvArgs* args, int out_dtype, int n_t
         && a.partial_row_stride >= ((in_width + 3) & ~3LL)
         && ((uintptr_t)a.out % 16 == 0) && (a.out_row_stride * el) % 16 == 0
         && (a.q_norm_w == nullptr || (uintptr_t)a.q_norm_w % 16 == 0) && (a.k_norm_w == nullptr || (uintptr_t)a.k_norm_w % 16 == 0)
-        && (a.k_pool == nullptr || ((uintptr_t)a.k_pool % 16 == 0 && (uintptr_t)a.v_pool % 16 == 0));
+        && (a.k_pool == nullptr || ((uintptr_t)a.k_pool % 16 == 0 && (uintptr_t)a.v_pool % 16 == 0))
+        && (a.bias == nullptr || (uintptr_t)a.bias % 16 == 0);
     // few tokens (a decode step) leave most of the GPU idle and are a chain of memory waits: four times the threads a
     // token shorten the chain; many tokens fill the GPU with blocks of 256
     const int threads = n_tokens <= 2 * 148 ? 1024 : 256;
@@ -321,5 +331,34 @@ extern "C" int tb_head_gate(void* o, int dtype, const float* gate, int n_tokens,
         return tb_launch_status();
     }
     TB_DISPATCH_1(dtype, T, tb_launch(head_gate_kernel<T>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (T*)o, gate, n, D));
+    return tb_launch_status();
+}
+
+// One warp per (token, head): in [rows][2][D] -> out [rows][D], the difference and its unit norm in 32-bit.
+template <typename T>
+__global__ void head_difference_kernel(const T* __restrict__ in, T* __restrict__ out, long long rows, int D, int vdim,
+                                       float lam, float eps, float out_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int lane = threadIdx.x & 31;
+    const T* a1 = in + r * 2 * D;
+    const T* a2 = a1 + D;
+    float sq = 0.f;
+    for (int d = lane; d < vdim; d += 32) { const float o = to_f<T>(a1[d]) - lam * to_f<T>(a2[d]); sq = fmaf(o, o, sq); }
+    const float f = out_scale / sqrtf(warp_sum(sq) / (float)vdim + eps);
+    T* o_row = out + r * D;
+    for (int d = lane; d < D; d += 32)
+        o_row[d] = from_f<T>(d < vdim ? (to_f<T>(a1[d]) - lam * to_f<T>(a2[d])) * f : 0.f);
+}
+
+extern "C" int tb_head_difference(const void* in, void* out, int dtype, int n_tokens, int n_heads, int D, int vdim, float lam,
+                                  float eps, float out_scale, cudaStream_t stream) {
+    const long long rows = (long long)n_tokens * n_heads;
+    if (rows <= 0) return 0;
+    if (D <= 0 || vdim <= 0 || vdim > D) return tb_refuse("head_difference: D=%d vdim=%d", D, vdim);
+    TB_DISPATCH_1(dtype, T, tb_launch(head_difference_kernel<T>, dim3((unsigned)((rows + 3) / 4)), dim3(128), 0, stream,
+                                      (const T*)in, (T*)out, rows, D, vdim, lam, eps, out_scale));
     return tb_launch_status();
 }

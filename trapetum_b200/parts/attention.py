@@ -49,6 +49,15 @@ the attention kernel (``ops.projnorm_kv``), all in 32-bit:
   ``sigmoid(G x)[h]`` before the output projection; its rows ride in the fused
   projection.
 
+Three more options change who sees whom and how the scores become weights; they ride on the same path
+(``ops.projnorm_kv``, which then also adds the biases), and their attention kernels are ``ops.attn_mixed_*``:
+
+* ``block`` B (instead of ``window``): the query at position i sees key j iff ``j <= i`` and both lie in the same
+  block of B positions, blocks counted from position 0 of the sequence; the cache line is a ring of B rows;
+* ``unit_sink``: the softmax denominator also holds ``exp(0)``, a sink without a key and without a value;
+* ``talk`` (a tensor name, [heads, heads]): the heads' scores are mixed before the mask and the softmax,
+  ``s_h <- sum_g talk[h, g] s_g``.  Scale and ``head_temp`` are folded into the matrix when the weights are bound.
+
 The three projections are fused into one matrix when the weights are bound, so
 a step runs one product for q, k and v.
 """
@@ -111,16 +120,26 @@ class Attention(Mixer):
         self.proj_norm_eps = float(pn.get("eps", 0.0))
         self.head_temp_name = p.get("head_temp")
         self.out_gate_name = p.get("out_gate")
-        self.projected = bool(self.proj_norm_names or self.head_temp_name or self.out_gate_name or self.vd != self.hd)
+        self.block = int(p["block"]) if p.get("block") else None
+        self.unit_sink = bool(p.get("unit_sink"))
+        self.talk_name = p.get("talk")
+        self.mixed = bool(self.block or self.unit_sink or self.talk_name)
+        if self.block and self.window:
+            raise ValueError("attention: 'block' and 'window' exclude each other")
+        if self.block is not None and self.block < 1:
+            raise ValueError(f"attention: block={self.block} must be positive")
+        self.projected = bool(self.proj_norm_names or self.head_temp_name or self.out_gate_name or self.vd != self.hd
+                              or self.mixed)
         if self.projected:
-            if self.prepared or self.bias_names or self.q_norm or self.k_norm or self.softcap:
-                raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim' and 'out_gate' go without biases, head "
-                                 "norms, a cap, 'v' None, 'head_unit_norm' and 'q_temp'")
+            if self.prepared or self.q_norm or self.k_norm or self.softcap:
+                raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim', 'out_gate', 'block', 'unit_sink' and 'talk' "
+                                 "go without head norms, a cap, 'v' None, 'head_unit_norm' and 'q_temp'")
             if self.position.rotary_table() is None:
                 raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim' and 'out_gate' go with a rotate-half "
                                  "rotation or with no position encoding")
-            self.pad = ops.attn_padded_head(rt.dtype, max(self.hd, self.vd))
-        self.wq_norm = self.wk_norm = self.head_temp = self.w_o_padded = None
+            # the mixing kernels take any head size; the tensor-core kernels want one of theirs
+            self.pad = (max(self.hd, self.vd) + 7) // 8 * 8 if self.mixed else ops.attn_padded_head(rt.dtype, max(self.hd, self.vd))
+        self.wq_norm = self.wk_norm = self.head_temp = self.w_o_padded = self.mix = self.b_proj = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {
@@ -137,7 +156,9 @@ class Attention(Mixer):
             specs[self.prefix + self.head_temp_name] = TensorSpec((self.n_heads,), "gain")
         if self.out_gate_name:
             specs[self.prefix + self.out_gate_name] = TensorSpec((self.n_heads, self.hidden))
-        sizes = {"q": self.qd, "k": self.kvd, "v": self.kvd, "o": self.hidden}
+        if self.talk_name:
+            specs[self.prefix + self.talk_name] = TensorSpec((self.n_heads, self.n_heads))
+        sizes = {"q": self.qd, "k": self.kvd, "v": self.n_kv * self.vd, "o": self.hidden}
         for key, name in self.bias_names.items():
             specs[self.prefix + name] = TensorSpec((sizes[key],))
         for n in (self.q_norm, self.k_norm):
@@ -160,6 +181,19 @@ class Attention(Mixer):
                 self.wk_norm = tensors[self.prefix + self.proj_norm_names["k"]].float().contiguous()
             if self.head_temp_name:
                 self.head_temp = tensors[self.prefix + self.head_temp_name].float().contiguous()
+            if self.mixed:
+                # s_h = sum_g talk[h, g] * temp[g] * scale * (q_g . k): one 32-bit matrix
+                mix = tensors[self.prefix + self.talk_name].float() if self.talk_name \
+                    else torch.eye(self.n_heads, dtype=torch.float32, device=q.device)
+                if self.head_temp is not None:
+                    mix = mix * self.head_temp[None, :]
+                self.mix = (mix * self.scale).contiguous()
+            if any(key in self.bias_names for key in "qkv"):
+                parts = [tensors[self.prefix + self.bias_names[key]].float() if key in self.bias_names
+                         else torch.zeros(m, dtype=torch.float32, device=q.device)
+                         for key, m in (("q", self.qd), ("k", self.kvd), ("v", self.n_kv * self.vd))]
+                parts.append(torch.zeros(n - sum(x.numel() for x in parts) + (-n % 16), dtype=torch.float32, device=q.device))
+                self.b_proj = torch.cat(parts).contiguous()
             w_o = tensors[self._name("o")]
             if self.pad != self.vd:
                 wide = torch.zeros((self.hidden, self.n_heads, self.pad), dtype=w_o.dtype, device=w_o.device)
@@ -170,7 +204,7 @@ class Attention(Mixer):
         self.w_qkv = torch.cat([m.to(dt) for m in mats], dim=0).contiguous()
         self.w_o = self.w_o_padded if self.projected else tensors[self._name("o")]
         self.position.bind(tensors)
-        if any(key in self.bias_names for key in "qkv"):
+        if not self.projected and any(key in self.bias_names for key in "qkv"):
             # one bias row for the fused projection, 32-bit; a projection without a bias of its own gets zeros
             parts = [tensors[self.prefix + self.bias_names[key]].float() if key in self.bias_names
                      else torch.zeros(n, dtype=torch.float32, device=q.device)
@@ -206,6 +240,8 @@ class Attention(Mixer):
         return part
 
     def kernel_files(self):
+        if self.mixed:
+            return linear_kernels(self.rt.dtype) + ("projnorm_kv", "attention_mixed") + (("activation",) if "o" in self.bias_names else ())
         if self.projected:
             fast = ("projnorm_kv",)
             if ops.attn_decode_takes(self.rt.dtype, self.n_heads, self.n_kv, self.pad):
@@ -230,7 +266,7 @@ class Attention(Mixer):
         return linear_kernels(self.rt.dtype) + self.position.kernel_files() + ("attention_simt",) + fast
 
     def cache_need(self):
-        return KVNeed(self.n_kv, self.pad if self.projected else self.hd, self.window)
+        return KVNeed(self.n_kv, self.pad if self.projected else self.hd, self.block or self.window)
 
     def forward(self, x, ctx, line):
         dt = self.rt.dtype
@@ -311,12 +347,20 @@ class Attention(Mixer):
         inv_freq, rotary = self.position.rotary_table()
         part = linear_partials(x, self.w_qkv)
         qkv, gate = ops.projnorm_kv(part, H, G, self.hd, self.vd, D, dt, self.wq_norm, self.wk_norm, self.proj_norm_eps,
-                                    self.head_temp, rotary, inv_freq, bool(self.out_gate_name), ctx.positions,
-                                    ctx.token_seq, ctx.len_after, line.k, line.v, line.page_table, line.ring_rows)
+                                    None if self.mixed else self.head_temp, rotary, inv_freq, bool(self.out_gate_name),
+                                    ctx.positions, ctx.token_seq, ctx.len_after, line.k, line.v, line.page_table,
+                                    line.ring_rows, self.b_proj)
         q = qkv[:, :H * D]
         k = qkv[:, H * D:(H + G) * D]
         v = qkv[:, (H + G) * D:]
-        if ctx.is_prefill:
+        if self.mixed:
+            seen = -self.block if self.block else (self.window or 0)
+            if ctx.is_prefill:
+                o = ops.attn_mixed_prefill(q, k, v, ctx.seq_start, ctx.token_seq, H, G, D, self.mix, seen, self.unit_sink)
+            else:
+                o = ops.attn_mixed_decode(q, line.k, line.v, line.page_table, ctx.len_after, H, G, D, self.mix, seen,
+                                          self.unit_sink, line.ring_rows, ctx.len_bucket)
+        elif ctx.is_prefill:
             o = ops.attn_prefill(q, k, v, ctx.seq_start, ctx.token_seq, H, G, D, self.scale, 0.0, self.window or 0,
                                  ctx.max_seq_len, ctx.seq_lens, ctx.memo)
         else:
@@ -324,7 +368,7 @@ class Attention(Mixer):
                                 self.window or 0, line.ring_rows, ctx.len_bucket, ctx.uneven)
         if gate is not None:
             ops.head_gate(o, gate, H)
-        return linear_partials(o, self.w_o)
+        return self._out(o)
 
 
 register_part("mixer", "attention", Attention)

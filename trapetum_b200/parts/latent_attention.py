@@ -23,6 +23,18 @@ latents back through ``W_uv``.  Both are the same function of the same cached ro
 Parameters (none is fixed in code): ``hidden_size``, ``heads``, ``plain_dim``, ``rot_dim``, ``value_dim``,
 ``kv_rank``, ``scale``, ``rotary_dims``, ``theta``, ``eps`` and the tensor names ``q``, ``dkv``, ``dkv_norm``,
 ``uk``, ``uv``, ``o``, ``sink`` (None: a plain softmax).
+
+Optional:
+
+* ``q_latent`` ``{"rank", "down", "norm", "up"}`` (instead of ``q``): the queries go through a latent of their own,
+  ``c_q = rmsnorm(W_down h) * norm`` (the layer's eps), ``q = W_up c_q``; the down product rides with ``dkv``'s;
+* ``rotary`` ``{"dims", "base", "scaling", "pairing"}`` (instead of ``rotary_dims`` / ``theta``): ``scaling`` as
+  :func:`~trapetum_b200.parts.rope.rotary_frequencies` takes it; ``pairing`` "halves" (i, i + dims/2) or "neighbours"
+  (2i, 2i + 1).  Neighbours are a matter of the weights' row order: the rows that make the rotated numbers of q and
+  of ``r`` are sorted evens first when the weights are bound, which turns the pairing into halves and changes no
+  dot product.  The factor that a blended scaling puts on cos and sin is applied twice to ``r`` and not to q;
+* ``window`` W: the query at position i sees j iff ``0 <= i - j < W``; the cache line is then a ring;
+* ``out_gate`` (a tensor name, [heads, hidden]): head h's output times ``sigmoid(G h)[h]``; its rows ride with ``dkv``'s.
 """
 from __future__ import annotations
 
@@ -35,6 +47,7 @@ from ..weights.loader import TensorSpec
 from .base import KVNeed, Mixer, register_part
 from .linear import kernel_files as linear_kernels
 from .linear import linear, linear_partials
+from .rope import rotary_frequencies
 
 
 def _round_up(n: int, m: int) -> int:
@@ -54,9 +67,17 @@ class LatentAttention(Mixer):
         self.V = int(p["value_dim"])
         self.C = int(p["kv_rank"])
         self.scale = float(p["scale"])
-        self.rot_dims = int(p.get("rotary_dims", self.R))
-        self.theta = float(p["theta"])
+        rot = p.get("rotary")
+        self.rot_dims = int(rot["dims"]) if rot else int(p.get("rotary_dims", self.R))
+        self.theta = float(rot["base"]) if rot else float(p["theta"])
+        self.neighbours = bool(rot) and rot.get("pairing", "halves") == "neighbours"
+        if rot and rot.get("pairing", "halves") not in ("halves", "neighbours"):
+            raise ValueError(f"latent_attention: pairing '{rot.get('pairing')}' is neither 'halves' nor 'neighbours'")
         self.eps = float(p["eps"])
+        self.window = int(p["window"]) if p.get("window") else None
+        self.q_latent = dict(p["q_latent"]) if p.get("q_latent") else None
+        self.Q = int(self.q_latent["rank"]) if self.q_latent else 0
+        self.out_gate_name = p.get("out_gate")
         if self.rot_dims % 2 or not (0 <= self.rot_dims <= self.R):
             raise ValueError(f"latent_attention: rotary_dims {self.rot_dims} must be even and at most rot_dim {self.R}")
         # the prefill kernels want one head size for q, k and v: the larger of the two, a multiple of 16; the
@@ -66,12 +87,15 @@ class LatentAttention(Mixer):
             # the tcgen05 kernel takes 64, 128 and 256: more padding, a faster kernel
             self.hd = next((n for n in (64, 128, 256) if n >= self.hd), self.hd)
         self.has_sink = p.get("sink") is not None
-        idx = torch.arange(0, self.rot_dims, 2, dtype=torch.float32)
-        self._inv_freq_cpu = 1.0 / (torch.tensor(self.theta, dtype=torch.float32) ** (idx / max(self.rot_dims, 1)))
+        self.rot_mult = 1.0
+        if rot:
+            self._inv_freq_cpu, self.rot_mult = rotary_frequencies(self.rot_dims, self.theta, rot.get("scaling"))
+        else:
+            idx = torch.arange(0, self.rot_dims, 2, dtype=torch.float32)
+            self._inv_freq_cpu = 1.0 / (torch.tensor(self.theta, dtype=torch.float32) ** (idx / max(self.rot_dims, 1)))
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         specs = {
-            self._name("q"): TensorSpec((self.H * (self.D + self.R), self.hidden)),
             self._name("dkv"): TensorSpec((self.C + self.R, self.hidden)),
             self._name("dkv_norm"): TensorSpec((self.C,), "gain"),
             self._name("uk"): TensorSpec((self.H * self.D, self.C)),
@@ -80,20 +104,49 @@ class LatentAttention(Mixer):
         }
         if self.has_sink:
             specs[self._name("sink")] = TensorSpec((self.H,), "norm")
+        if self.q_latent:
+            ql = self.q_latent
+            specs[self.prefix + ql["down"]] = TensorSpec((self.Q, self.hidden))
+            specs[self.prefix + ql["norm"]] = TensorSpec((self.Q,), "gain")
+            specs[self.prefix + ql["up"]] = TensorSpec((self.H * (self.D + self.R), self.Q))
+        else:
+            specs[self._name("q")] = TensorSpec((self.H * (self.D + self.R), self.hidden))
+        if self.out_gate_name:
+            specs[self.prefix + self.out_gate_name] = TensorSpec((self.H, self.hidden))
         return specs
 
     def bind(self, tensors) -> None:
         H, D, R, V, C, hd = self.H, self.D, self.R, self.V, self.C, self.hd
-        wq = tensors[self._name("q")]
+        wq = tensors[self.prefix + self.q_latent["up"]] if self.q_latent else tensors[self._name("q")]
         dt, dev = wq.dtype, wq.device
+        q_in = wq.shape[1]
+        # the order in which the rotated numbers are made: neighbours (2i, 2i + 1) become halves (i, i + dims/2)
+        order = torch.arange(R, device=dev)
+        if self.neighbours:
+            order = torch.cat([torch.arange(0, self.rot_dims, 2, device=dev), torch.arange(1, self.rot_dims, 2, device=dev),
+                               torch.arange(self.rot_dims, R, device=dev)])
         # queries head by head as [rot | plain | zeros]: the rotation kernel turns the FIRST dims of a head, and a dot
         # product does not care in which order q and k list their dims as long as they agree
-        q3 = wq.view(H, D + R, self.hidden)
-        wq_p = torch.zeros((H, hd, self.hidden), dtype=dt, device=dev)
-        wq_p[:, :R] = q3[:, D:]
+        q3 = wq.view(H, D + R, q_in)
+        wq_p = torch.zeros((H, hd, q_in), dtype=dt, device=dev)
+        wq_p[:, :R] = q3[:, D:][:, order]
         wq_p[:, R:R + D] = q3[:, :D]
-        self.w_q = wq_p.view(H * hd, self.hidden).contiguous()
-        self.w_dkv = tensors[self._name("dkv")]
+        self.w_q = wq_p.view(H * hd, q_in).contiguous()
+        w_dkv = tensors[self._name("dkv")]
+        if self.neighbours:
+            w_dkv = torch.cat([w_dkv[:C], w_dkv[C:][order]], dim=0)
+        # what rides with the down projection: the queries' latent and the heads' gates, rows of zeros up to 16
+        rows = [w_dkv]
+        self.w_cq_norm = None
+        if self.q_latent:
+            rows.append(tensors[self.prefix + self.q_latent["down"]].to(w_dkv.dtype))
+            self.w_cq_norm = tensors[self.prefix + self.q_latent["norm"]].float().contiguous()
+        if self.out_gate_name:
+            rows.append(tensors[self.prefix + self.out_gate_name].to(w_dkv.dtype))
+        if len(rows) > 1:
+            n = sum(r.shape[0] for r in rows)
+            rows.append(torch.zeros((-n % 16, self.hidden), dtype=w_dkv.dtype, device=dev))
+        self.w_dkv = torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else w_dkv.contiguous()
         self.w_c_norm = tensors[self._name("dkv_norm")].float().contiguous()
         uk = tensors[self._name("uk")].to(dt).view(H, D, C)
         uv = tensors[self._name("uv")].to(dt).view(H, V, C)
@@ -125,10 +178,11 @@ class LatentAttention(Mixer):
             fast = (ops.attn_prefill_tc_lib(self.hd),)
         elif ops.attn_prefill_takes(self.rt.dtype, self.hd):
             fast = (ops.attn_prefill_lib(self.hd),)
-        return linear_kernels(self.rt.dtype) + ("rope_kv", "attention_latent", "attention_simt") + fast
+        return linear_kernels(self.rt.dtype) + ("rope_kv", "attention_latent", "attention_simt") + fast \
+            + (("projnorm_kv",) if self.out_gate_name else ())
 
     def cache_need(self):
-        return KVNeed(1, self.C + self.R, None, values=False)
+        return KVNeed(1, self.C + self.R, self.window, values=False)
 
     def forward(self, x, ctx, line):
         dt = self.rt.dtype
@@ -136,22 +190,33 @@ class LatentAttention(Mixer):
         if not line.owner:
             raise NotImplementedError("latent_attention: reading another call's cache is not built")
         part = linear_partials(x, self.w_dkv)             # 32-bit sums: they enter a norm and a rotation
-        rows = ops.latent_rows(part, self.w_c_norm, self.eps, self.inv_freq, self.rot_dims, C, R, ctx.positions,
-                               ctx.token_seq, line.k, line.page_table, dt)
+        gate = None
+        if self.q_latent or self.out_gate_name:
+            rows, cq, gate = ops.latent_rows(part, self.w_c_norm, self.eps, self.inv_freq, self.rot_dims, C, R, ctx.positions,
+                                             ctx.token_seq, line.k, line.page_table, dt, line.ring_rows, ctx.len_after,
+                                             self.rot_mult * self.rot_mult, self.w_cq_norm,
+                                             H if self.out_gate_name else 0)
+        else:
+            cq = None
+            rows = ops.latent_rows(part, self.w_c_norm, self.eps, self.inv_freq, self.rot_dims, C, R, ctx.positions,
+                                   ctx.token_seq, line.k, line.page_table, dt, line.ring_rows, ctx.len_after,
+                                   self.rot_mult * self.rot_mult)
         # the queries: 32-bit sums in, rotated and rounded once
-        q_part = linear_partials(x, self.w_q)
+        q_part = linear_partials(cq if self.q_latent else x, self.w_q)
         q = torch.empty(q_part.shape[1:], dtype=dt, device=x.device)
         ops.rope_kv(q, H, 0, hd, self.rot_dims, self.inv_freq if self.rot_dims else None, ctx.positions, ctx.token_seq,
                     ctx.len_after, None, None, None, 0, q_part)
         if ctx.is_prefill:
             kv = linear(rows, self.w_up, dt)              # [T, 2 H hd]: every head's keys, then every head's values
             o = ops.attn_prefill_sink(q, kv[:, :H * hd], kv[:, H * hd:], ctx.seq_start, ctx.token_seq, H, hd, self.scale,
-                                      self.sink, ctx.max_seq_len, ctx.seq_lens)
+                                      self.sink, ctx.max_seq_len, ctx.seq_lens, self.window or 0)
         else:
             ql = ops.head_linear(q, self.w_qmap, H)       # [B, H (C + R)]
             ol = ops.latent_decode(ql, line.k, line.page_table, ctx.len_after, self.sink, H, C, R, self.scale,
-                                   ctx.len_bucket)
+                                   ctx.len_bucket, self.window or 0, line.ring_rows)
             o = ops.head_linear(ol, self.w_vmap, H)       # [B, H hd]
+        if gate is not None:
+            ops.head_gate(o, gate, H)
         return linear_partials(o, self.w_o)
 
 

@@ -19,6 +19,35 @@ from ..csrc import ops
 from .base import PositionEncoding, register_part
 
 
+def rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
+    """(frequencies float32 [dims / 2], factor on cos and sin) of a rotation over ``dims`` numbers.
+
+    ``f_i = base^(-2i / dims)``.  ``scaling`` None: as they are.  ``{"factor": s}``: every frequency divided by s (linear
+    position scaling).  ``{"factor": s, "original": L, "fast": a, "slow": b}``: a blend per frequency between ``f_i``
+    (dims that turn more than ``a`` times over L positions) and ``f_i / s`` (dims that turn fewer than ``b`` times):
+    with ``d(t) = dims * ln(L / (2 pi t)) / (2 ln base)``, ``lo = max(floor(d(a)), 0)``, ``hi = min(ceil(d(b)), dims - 1)``
+    and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` the frequency is ``f_i / s * ramp_i + f_i * (1 - ramp_i)``,
+    and cos and sin come times ``0.1 ln(s) + 1``.  Computed in 64-bit, stored in 32."""
+    import math
+    half = dims // 2
+    f = [float(base) ** (-2.0 * i / dims) for i in range(half)]
+    mult = 1.0
+    sc = dict(scaling or {})
+    if "original" in sc:
+        s, L = float(sc["factor"]), float(sc["original"])
+
+        def dim_of(turns):
+            return dims * math.log(L / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+        lo = max(math.floor(dim_of(float(sc["fast"]))), 0)
+        hi = min(math.ceil(dim_of(float(sc["slow"]))), dims - 1)
+        ramp = [min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0) for i in range(half)]
+        f = [x / s * r + x * (1.0 - r) for x, r in zip(f, ramp)]
+        mult = 0.1 * math.log(s) + 1.0
+    elif sc.get("factor"):
+        f = [x / float(sc["factor"]) for x in f]
+    return torch.tensor(f, dtype=torch.float64).to(torch.float32), mult
+
+
 class Rope(PositionEncoding):
     def __init__(self, params, prefix, rt):
         super().__init__(params, prefix, rt)
