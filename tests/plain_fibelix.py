@@ -213,14 +213,17 @@ def difference_attention(h, m, t, p, eps, first_pos=0, past=None, rnd=same, sour
     out = []
     for g in range(H):
         kv = g // (H // G)
-        a = [softmax_seen(q[:, g, i] @ k[:, kv, i].T * m["scale"], ok) @ v[:, kv] for i in range(2)]
+        # a 16-bit engine stores each map's output (and its tensor-core kernels the weights that meet v)
+        a = [rnd(rnd(softmax_seen(q[:, g, i] @ k[:, kv, i].T * m["scale"], ok)) @ v[:, kv]) for i in range(2)]
         o = a[0] - lam * a[1]
         out.append(o / rms(o, eps) * (1.0 - m["diff"]))
     o = rnd(torch.cat(out, dim=-1))
     return o @ f64(t[p + "o"]).T
 
 
-def latent_attention(h, m, t, p, eps, first_pos=0, past=None, rnd=same):
+def latent_attention(h, m, t, p, eps, first_pos=0, past=None, rnd=same, mapped=False):
+    """``mapped``: the same sums in the order in which an engine that reads the cached latents directly makes them (the
+    query mapped into the latent's space, the weighted sum of latents mapped back); it matters to ``rnd`` only."""
     H, D, R, V, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     T = h.shape[0]
     pos = torch.arange(first_pos, first_pos + T)
@@ -242,9 +245,14 @@ def latent_attention(h, m, t, p, eps, first_pos=0, past=None, rnd=same):
     gate = torch.sigmoid(h @ f64(t[p + "g"]).T)                     # [T, H]
     out = []
     for g in range(H):
-        s = (q[:, g, :D] @ (c @ uk[g].T).T + q[:, g, D:] @ r.T) * m["scale"]
-        w = softmax_seen(s, ok)
-        out.append((w @ (c @ uv[g].T)) * gate[:, g:g + 1])
+        if mapped:
+            s = (rnd(q[:, g, :D] @ uk[g]) @ c.T + q[:, g, D:] @ r.T) * m["scale"]
+            w = rnd(softmax_seen(s, ok))
+            out.append(rnd(rnd(w @ c) @ uv[g].T) * gate[:, g:g + 1])
+            continue
+        s = (q[:, g, :D] @ rnd(c @ uk[g].T).T + q[:, g, D:] @ r.T) * m["scale"]
+        w = rnd(softmax_seen(s, ok))
+        out.append(rnd(w @ rnd(c @ uv[g].T)) * gate[:, g:g + 1])
     o = rnd(torch.cat(out, dim=-1))
     return o @ f64(t[p + "o"]).T
 
@@ -260,6 +268,16 @@ def route(h, f, t, p):
     order = torch.sort(z, dim=-1, descending=True, stable=True).indices[:, :top]
     zs = torch.gather(z, 1, order)
     return order, torch.softmax(zs, dim=-1), z
+
+
+def route_margin(h, f, t, p):
+    """Per token: how far the last winner's logit lies above the best loser's (infinite when every expert wins)."""
+    z = route(h, f, t, p)[2]
+    top = f["router"]["top"]
+    zs = torch.sort(z, dim=-1, descending=True).values
+    if top >= z.shape[1]:
+        return torch.full((h.shape[0],), math.inf, dtype=F)
+    return zs[:, top - 1] - zs[:, top]
 
 
 def experts(h, f, t, p, rnd=same):
@@ -286,12 +304,14 @@ class Sequence:
         self.n = 0
         self.past: List[dict] = [{} for _ in cfg["layers"]]
         self.streams: List[torch.Tensor] = []          # after the last piece: the stream after every layer
+        self.margins: List[torch.Tensor] = []          # per piece: every token's smallest routing margin over the layers
 
     def feed(self, tokens) -> torch.Tensor:
         cfg, t, rnd = self.cfg, self.t, self.rnd
         eps = cfg["norm"]["eps"]
         x = f64(t["embed"])[torch.as_tensor(tokens, dtype=torch.long)]
         self.streams = []
+        margin = torch.full((len(tokens),), math.inf, dtype=F)
         for i, L in enumerate(cfg["layers"]):
             p, m = f"l{i}.", L["mixer"]
             h = rnd(offset_norm(x, f64(t[p + "norm1"]), eps))
@@ -301,13 +321,16 @@ class Sequence:
                 src = self.past[m["kv_from"]] if m.get("kv_from") is not None else None
                 y = difference_attention(h, m, t, p + "mix.", eps, self.n, self.past[i], rnd, src)
             elif L["type"] == "latent_attention":
-                y = latent_attention(h, m, t, p + "mix.", eps, self.n, self.past[i], rnd)
+                y = latent_attention(h, m, t, p + "mix.", eps, self.n, self.past[i], rnd, mapped=self.n > 0)
             else:
                 raise ValueError(L["type"])
             x = x + y
             if L.get("mlp") is not None:
-                x = x + experts(rnd(offset_norm(x, f64(t[p + "norm2"]), eps)), L["mlp"], t, p + "mlp.", rnd)
+                h2 = rnd(offset_norm(x, f64(t[p + "norm2"]), eps))
+                margin = torch.minimum(margin, route_margin(h2, L["mlp"], t, p + "mlp."))
+                x = x + experts(h2, L["mlp"], t, p + "mlp.", rnd)
             self.streams.append(x.clone())
+        self.margins.append(margin)
         self.n += len(tokens)
         return rnd(offset_norm(x, f64(t["final.norm"]), eps)) @ f64(t["embed"]).T
 
@@ -320,3 +343,24 @@ def logits(cfg, tensors, tokens, pieces=None, rnd=same) -> torch.Tensor:
         out.append(seq.feed(tokens[at:at + n]))
         at += n
     return torch.cat(out)
+
+
+def forward(cfg, tensors, tokens, rnd=same) -> torch.Tensor:
+    return logits(cfg, tensors, tokens, None, rnd)
+
+
+def routing_margins(cfg, tensors, tokens) -> torch.Tensor:
+    seq = Sequence(cfg, tensors)
+    seq.feed(tokens)
+    return seq.margins[0]
+
+
+def generate_greedy(cfg, tensors, prompt, n: int) -> List[int]:
+    """``n`` tokens after ``prompt``, each the first of the largest logits."""
+    seq = Sequence(cfg, tensors)
+    nxt = int(torch.argmax(seq.feed(prompt)[-1]))
+    out = [nxt]
+    while len(out) < n:
+        nxt = int(torch.argmax(seq.feed([nxt])[-1]))
+        out.append(nxt)
+    return out

@@ -85,7 +85,8 @@ def fibelix_spec(cfg: FibelixConfig) -> ModelSpec:
         else:
             ffn = PartSpec("none", {})
         block = PartSpec("pre_norm", {"pre_mixer_norm": norm("norm1"),
-                                      "pre_ffn_norm": norm("norm2") if L.mlp is not None else None})
+                                      "pre_ffn_norm": norm("norm2") if L.mlp is not None else None,
+                                      "idle": {} if L.mlp is not None else {"norm2": W}})
         layers.append(LayerSpec(block=block, mixer=mixer, feed_forward=ffn, prefix=f"l{i}."))
 
     schedule = []

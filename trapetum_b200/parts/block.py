@@ -88,6 +88,14 @@ class PreNormBlock(_NormedBlock):
         self.norms = {n: build_part("norm", params[n], prefix, rt) for n in self.NORMS
                       if n == "pre_mixer_norm" or self.has_ffn}
 
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        specs = super().tensor_specs()
+        # ``idle``: tensor name -> size of vectors that a file may carry for a layer without feed-forward (the norm
+        # that nothing follows); they are accepted and not used
+        for name, size in (self.params.get("idle") or {}).items():
+            specs.setdefault(self.prefix + name, TensorSpec((int(size),), "norm", optional=True))
+        return specs
+
     def forward(self, stream, ctx, cache) -> None:
         dt = self.rt.dtype
         x = stream.normed(self.norms["pre_mixer_norm"], dt)
