@@ -21,6 +21,7 @@ MEASURED_PEAKS.json beside this file when the driver wrote it, otherwise from th
     python bench.py --design divanex [--sizes small,medium,large] [--batch 8] [--context 2048]
     python bench.py --design lofirax [--sizes small,medium,large] [--batch 8] [--context 2048]
     python bench.py --design fidepel [--sizes small,medium,large] [--batch 8] [--context 2048]
+    python bench.py --design fibelix [--sizes small,medium,large] [--batch 8] [--context 2048]
 
 ``--design divanex`` is a measurement of its own (the default workload and its line stay as they are): Divanex
 models with random weights at a few layer sizes, a 2,048-token prompt and decode steps of ``batch`` sequences
@@ -799,6 +800,223 @@ def fidepel_compare(args, torch):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# --design fibelix: the design at sizes that resemble real layers, beside Fidepel (the closest model of the library:
+# rotary attention with a number per head, a mask that bounds what a query sees, values of their own size, and
+# softmax-routed experts, on the same host) at equal width, depth, head counts, head size and vocabulary
+# ---------------------------------------------------------------------------------------------------------------
+# name -> (blocks of the mixed attention, blocks of the difference attention, window of the latent attention,
+#          latent: rotated dims, kv rank, q rank; experts, top, expert ff); the rest are DESIGN_SIZES'
+FIBELIX_SIZES = {"small": (1024, 512, 1024, 64, 448, 768, 16, 4, 512),
+                 "medium": (1024, 512, 1024, 64, 448, 1024, 32, 4, 1024),
+                 "large": (1024, 512, 1024, 64, 448, 1536, 32, 4, 2048)}
+
+
+def fibelix_config(size):
+    W, L, H, G, d, _, _, _, _, V = DESIGN_SIZES[size]
+    blk, blk2, win, R, C, Q, E, top, eff = FIBELIX_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}}
+    layers, last_own = [], None
+    for i in range(L):
+        kind = i % 3
+        if kind == 0:
+            layer = {"type": "latent_attention",
+                     "mixer": {"heads": H, "dim": d, "rot_dim": R, "vdim": d, "kv_rank": C, "q_rank": Q, "scale": (d + R) ** -0.5,
+                               "mask": {"size": win},
+                               "rot": {"dims": R, "base": 10000.0, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+        elif kind == 1:
+            layer = {"type": "attention",
+                     "mixer": {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": blk},
+                               "rot": {"dims": d // 2, "base": 500000.0, "scaling": {"factor": 8.0}}}}
+        else:
+            m = {"heads": H // 2, "kv_heads": G, "dim": d // 2, "vdim": d, "scale": (d // 2) ** -0.5, "diff": 0.6,
+                 "mask": {"size": blk2}}
+            if last_own is None:
+                last_own = i
+            else:
+                m["kv_from"], last_own = last_own, None          # every second one reads the one before it
+            layer = {"type": "attention_2", "mixer": m}
+        layer["mlp"] = mlp
+        layers.append(layer)
+    return {"architecture": "Fibelix", "vocab": V, "width": W, "norm": {"eps": 1e-6}, "layers": layers}
+
+
+def fibelix_bytes_flops(cfg, tokens, ctx, batch):
+    """(weight bytes a decode step of ``batch`` sequences reads, with every matrix once and of the experts those that
+    ``batch`` tokens are expected to choose; cache bytes per sequence that a step at ``ctx`` tokens reads; tensor-core
+    FLOPs of one ``tokens``-token prompt, the (query, key) pairs that the masks leave)."""
+    W, V = cfg["width"], cfg["vocab"]
+    wb, cb, fl = V * W, 0, 2 * V * W * tokens
+
+    def pairs(span, blocks):
+        span = min(tokens, span or tokens)
+        if blocks:
+            full, rest = divmod(tokens, span)
+            return full * span * (span + 1) // 2 + rest * (rest + 1) // 2
+        return span * (span + 1) // 2 + (tokens - span) * span
+    for L in cfg["layers"]:
+        m, f = L["mixer"], L["mlp"]
+        H, D, Vd = m["heads"], m["dim"], m["vdim"]
+        size = (m.get("mask") or {}).get("size")
+        if L["type"] == "latent_attention":
+            R, C, Q = m["rot_dim"], m["kv_rank"], m["q_rank"]
+            per = (Q + C + R + H) * W + H * (D + R) * Q + H * (D + Vd) * C + W * H * Vd
+            cb += (C + R) * min(ctx, size or ctx) * 2
+            fl += 2 * H * (D + R + Vd) * pairs(size, False) + 2 * tokens * H * (D + Vd) * C
+        elif L["type"] == "attention":
+            G = m["kv_heads"]
+            per = (H * D + G * (D + Vd)) * W + W * H * Vd
+            seen = (ctx - 1) % size + 1 if size else ctx
+            cb += G * (D + Vd) * seen * 2
+            fl += 2 * H * (D + Vd) * pairs(size, True)
+        else:
+            G = m["kv_heads"]
+            own = m.get("kv_from") is None
+            per = H * 2 * D * W + (G * (2 * D + Vd) * W if own else 0) + W * H * Vd
+            seen = (ctx - 1) % size + 1 if size else ctx
+            cb += G * (2 * D + Vd) * seen * 2
+            fl += 2 * 2 * H * (D + Vd) * pairs(size, True)
+        used = per
+        if f:
+            E, top = f["router"]["experts"], f["router"]["top"]
+            one = 3 * f["expert"]["ff"] * W
+            used = per + E * W + top * one
+            per += E * W + one * E * (1.0 - (1.0 - top / E) ** batch)
+        wb += per
+        fl += 2 * tokens * used
+    return int(2 * wb), cb, fl, 0
+
+
+def fibelix_kernels(torch, size, hbm_gbs, tokens=PREFILL_TOKENS):
+    """The design's own kernels alone, each beside the like kernel of the closest model: microseconds, algorithmic
+    bytes (or FLOPs) and the fraction of the roofline.  One prompt of ``tokens`` tokens; 64 sequences at 2,048 for
+    the one-token kernels."""
+    from trapetum_b200.csrc import ops
+    W, _, H, G, d, _, _, _, _, _ = DESIGN_SIZES[size]
+    blk, blk2, win, R, C, Q, E, top, eff = FIBELIX_SIZES[size]
+    dev, bf = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    T = tokens
+    out = {}
+    tc_peak = peaks()[1]
+
+    def rec(name, us, nbytes, like=None, tensor_flops=0.0, fp32_flops=0.0):
+        t_mem, t_tc = nbytes / (hbm_gbs * 1e9) * 1e6, tensor_flops / (tc_peak * 1e12) * 1e6
+        t_fma = fp32_flops / (FP32_TFLOPS_NOMINAL * 1e12) * 1e6
+        best = max(t_mem, t_tc, t_fma)
+        out[name] = {"us": round(us, 1), "bytes": int(nbytes), "roofline_us": round(best, 1), "frac": round(best / us, 3),
+                     "bound": "tensor" if best == t_tc else ("fp32" if best == t_fma else "hbm")}
+        if like:
+            out[name]["like"] = like
+    rb = lambda *s: (torch.randn(*s, device=dev) * 0.5).to(bf)
+    pos = torch.arange(T, device=dev).int()
+    tseq = torch.zeros(T, device=dev).int()
+    ss = torch.tensor([0, T], device=dev).int()
+    # ---- prompts: scores mixed across heads (blocks, a unit sink) beside the plain attention kernel over the same blocks
+    q, k, v = rb(T, H * d), rb(T, G * d), rb(T, G * d)
+    mix = (torch.eye(H, device=dev) + 0.1 * torch.randn(H, H, device=dev)) * d ** -0.5
+    n_pairs = (T // blk) * blk * (blk + 1) // 2 + (T % blk) * (T % blk + 1) // 2
+    starts = torch.arange(0, T + 1, blk, device=dev).int()
+    lens = [blk] * (T // blk)
+    rec("attention with mixed scores (prefill)", _median_us(torch, lambda: ops.attn_mixed_prefill(q, k, v, ss, tseq, H, G, d, mix, -blk, True, T), flush),
+        (2 * H + 2 * G) * d * T * 2, like="attention (prefill)", tensor_flops=4.0 * H * d * n_pairs)
+    rec("attention (prefill)", _median_us(torch, lambda: ops.attn_prefill(q, k, v, starts, tseq, H, G, d, d ** -0.5, 0.0, 0, blk, lens), flush),
+        (2 * H + 2 * G) * d * T * 2, tensor_flops=4.0 * H * d * n_pairs)
+    # ---- difference attention: twice the heads at half the size over the same kernel, then the fold of the pairs
+    H2, d2 = H // 2, d // 2
+    qd, kd, vd_ = rb(T, 2 * H2 * d), rb(T, G * d), rb(T, G * d)
+    starts2 = torch.arange(0, T + 1, blk2, device=dev).int()
+    n_pairs2 = (T // blk2) * blk2 * (blk2 + 1) // 2
+    rec("difference attention (prefill: two maps a head)", _median_us(torch, lambda: ops.attn_prefill(qd, kd, vd_, starts2, tseq, 2 * H2, G, d, d2 ** -0.5, 0.0, 0, blk2, [blk2] * (T // blk2)), flush),
+        (4 * H2 + 2 * G) * d * T * 2, like="attention (prefill)", tensor_flops=4.0 * 2 * H2 * d * n_pairs2)
+    o2 = rb(T, 2 * H2 * d)
+    rec("head_difference", _median_us(torch, lambda: ops.head_difference(o2, H2, d, d, 0.55, 1e-6, 0.4), flush), 3 * H2 * d * T * 2, like="head_gate")
+    og, gate = rb(T, H * d), torch.rand(T, H, device=dev)
+    rec("head_gate", _median_us(torch, lambda: ops.head_gate(og, gate, H), flush), 2 * H * d * T * 2)
+    # ---- latent rows with the queries' latent and the gates, beside the rows alone
+    wide = C + R + Q + H
+    wide += -wide % 16
+    part, part0 = torch.randn(1, T, wide, device=dev), torch.randn(1, T, C + R, device=dev)
+    wc, wq = torch.ones(C, device=dev), torch.ones(Q, device=dev)
+    inv = torch.rand(R // 2, device=dev)
+    pool = torch.zeros((T // 64 + 1, 1, 64, C + R), dtype=bf, device=dev)
+    table = torch.arange(T // 64 + 1, device=dev).int()[None]
+    la = torch.tensor([T], device=dev).int()
+    rec("latent_rows with the queries' latent and gates", _median_us(torch, lambda: ops.latent_rows(part, wc, 1e-6, inv, R, C, R, pos, tseq, pool, table, bf, 0, la, 1.3, wq, H), flush),
+        T * ((C + R + Q + H) * 4 + (2 * (C + R) + Q) * 2 + H * 4), like="latent_rows")
+    rec("latent_rows", _median_us(torch, lambda: ops.latent_rows(part0, wc, 1e-6, inv, R, C, R, pos, tseq, pool, table, bf), flush),
+        T * (C + R) * (4 + 4))
+    # ---- one token for each of 64 sequences at 2,048
+    B, ctx = 64, 2048
+    pages = ctx // 64
+    lens_d = torch.full((B,), ctx, device=dev).int()
+    tab = torch.arange(B * pages, device=dev).int().view(B, pages)
+    kp, vp = rb(B * pages, G, 64, d), rb(B * pages, G, 64, d)
+    q1 = rb(B, H * d)
+    seen = (ctx - 1) % blk + 1
+    rec("attention with mixed scores (decode), 64 sequences", _median_us(torch, lambda: ops.attn_mixed_decode(q1, kp, vp, tab, lens_d, H, G, d, mix, -blk, True, 0, ctx), flush),
+        B * 2 * G * d * seen * 2, like="attention (decode) over the same blocks")
+    rec("attention (decode) over the same blocks", _median_us(torch, lambda: ops.attn_decode(q1, kp, vp, tab, lens_d, H, G, d, d ** -0.5, 0.0, -blk, 0, 2048), flush),
+        B * 2 * G * d * seen * 2)
+    lp = rb(B * pages, 1, 64, C + R)
+    ql = rb(B, H * (C + R))
+    rec("latent_decode through a window, 64 sequences", _median_us(torch, lambda: ops.latent_decode(ql, lp, tab, lens_d, None, H, C, R, 0.07, ctx, win, 0), flush),
+        B * (C + R) * min(win, ctx) * 2, like="latent_decode")
+    rec("latent_decode", _median_us(torch, lambda: ops.latent_decode(ql, lp, tab, lens_d, None, H, C, R, 0.07, ctx), flush),
+        B * (C + R) * ctx * 2)
+    return out
+
+
+def fibelix_compare(args, torch):
+    """Prints one JSON line: per size, Fibelix and the Fidepel model of equal width, depth, heads and vocabulary
+    (prefill of one 2,048-token prompt, decode at ``batch`` x ``context``), with bytes, FLOPs and roofline fractions,
+    and the design's kernels alone beside their like kernels."""
+    import trapetum_b200 as tb
+    from trapetum_b200.csrc import ops
+    hbm_gbs, bf16_tflops, peak_src = peaks()
+    warmup = max(3, args.warmup)
+    ctx, batch = args.context, args.batch
+    sizes = [s for s in args.sizes.split(",") if s in DESIGN_SIZES]
+    out = {"design": "fibelix", "beside": "fidepel", "sizes": {},
+           "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops, "source": peak_src},
+           "dtype": "bf16", "data": "synthetic (random weights, random token ids)", "batch": batch, "context": ctx,
+           "timing": "CUDA events; decode: median of five regions of --steps steps; kernels alone: a 256 MB buffer is written "
+                     "between timed launches (larger than L2)"}
+    clocks = ClockSampler()
+    clocks.__enter__()
+    for size in sizes:
+        row = {}
+        for which in ("fibelix", "fidepel"):
+            cfg = fibelix_config(size) if which == "fibelix" else fidepel_config(size)
+            V = cfg["vocab"]
+            model = tb.random_model(cfg, 7, 0.02, 0.1, "bfloat16", "cuda:0", host="python")
+            engine = tb.Engine(model, max_tokens=batch * (ctx + 64), max_slots=batch)
+            random_cache(engine)
+            pms, hms, wms = time_prefill(engine, torch, PREFILL_TOKENS, V, reps=5, warmup=warmup)
+            r = time_decode(engine, torch, [ctx] * batch, args.steps, warmup, V, clocks=clocks)
+            wb, cb, fl, _ = (fibelix_bytes_flops if which == "fibelix" else fidepel_bytes_flops)(cfg, PREFILL_TOKENS, ctx, batch)
+            nbytes = wb + batch * cb
+            pre_ideal = fl / (bf16_tflops * 1e12)
+            row[which] = {
+                "prefill": {"tokens": PREFILL_TOKENS, "ms": round(pms, 3), "tok_s": round(PREFILL_TOKENS * 1e3 / pms, 1),
+                            "tensor_flops": fl, "frac_of_roofline": round(pre_ideal * 1e3 / pms, 4)},
+                "decode": {"ms": r["ms"], "tok_s": round(batch * 1e3 / r["ms"], 1), "bytes": nbytes,
+                           "gbs": round(nbytes / (r["ms"] * 1e-3) / 1e9, 1),
+                           "frac_of_hbm": round(nbytes / (r["ms"] * 1e-3) / 1e9 / hbm_gbs, 4), "launches": r["launches"]},
+            }
+            engine.check_kernels()
+            del engine, model
+            torch.cuda.empty_cache()
+        if not args.no_points:
+            row["kernels_alone"] = fibelix_kernels(torch, size, hbm_gbs)
+        out["sizes"][size] = row
+    clocks.__exit__()
+    out["clocks"] = clocks.summary()
+    out["kernel_errors"] = ops.kernel_errors()
+    print(json.dumps(out))
+    return 0
+
+
 HOST = None              # which host runs the models (None: the library's default, the native host for these models)
 
 
@@ -1147,9 +1365,9 @@ def main() -> int:
     ap.add_argument("--leave-out", action="store_true",
                     help="instead of the bench line: the decode step re-timed with one kind of launch left out at a "
                          "time (its results are then wrong; only its time is of interest), one line per kind")
-    ap.add_argument("--design", default=None, choices=["divanex", "lofirax", "fidepel"],
+    ap.add_argument("--design", default=None, choices=["divanex", "lofirax", "fidepel", "fibelix"],
                     help="instead of the bench line: this design at the layer sizes of --sizes beside the library's closest "
-                         "model at equal size (divanex beside Gemma-2, lofirax beside divanex, fidepel beside Gemma-2)")
+                         "model at equal size (divanex beside Gemma-2, lofirax beside divanex, fidepel beside Gemma-2, fibelix beside fidepel)")
     ap.add_argument("--sizes", default="small,medium,large", help="with --design: which of small, medium, large")
     ap.add_argument("--gemm-compare", type=int, default=0, metavar="TOKENS",
                     help="instead of the bench line: the four products of a layer of --model at TOKENS tokens, this "
@@ -1173,6 +1391,8 @@ def main() -> int:
             args.context = 2048
         if args.design == "fidepel":
             return fidepel_compare(args, torch)
+        if args.design == "fibelix":
+            return fibelix_compare(args, torch)
         return lofirax_compare(args, torch) if args.design == "lofirax" else design_compare(args, torch)
     if args.gemm_compare:
         return gemm_compare(MODELS[args.model], torch, args.gemm_compare, peaks()[1])

@@ -146,7 +146,9 @@ def doubles(w: dict) -> dict:
 
 TOL32 = 3e-5
 ROUTING_MARGIN = 0.05          # logits of size 2 are sums of a few dozen products of 16-bit numbers; one of two experts may win
-ROUTING_TURNS = 0.005          # under this margin the 16-bit engine is taken to have chosen otherwise
+ROUTING_TURNS = 0.02           # under this margin the 16-bit engine is taken to have chosen otherwise (a token of one
+                               # configuration, margin 0.012, did: where one expert of four is chosen, every later token
+                               # that reads it differs)
 BF16_FLOOR, BF16_FACTOR = 2e-2, 3.0
 _BUDGET = {}
 

@@ -185,7 +185,7 @@ def mixed_attention(h, m, t, p, first_pos=0, past=None, rnd=same):
     ok = same_block(pos, kpos, _mask_size(m))
     out = []
     for g in range(H):
-        w = softmax_seen(s[g], ok, extra_one=True)
+        w = rnd(softmax_seen(s[g], ok, extra_one=True))       # tensor-core kernels round the weights that meet v
         out.append(w @ v[:, g // (H // G)])
     o = rnd(torch.cat(out, dim=-1))
     return o @ f64(t[p + "o"]).T + f64(t[p + "o.b"])

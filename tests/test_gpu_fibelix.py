@@ -27,7 +27,9 @@ PAGE = 64
 
 @pytest.fixture(scope="module")
 def weights():
-    return {name: random_weights(cfg, 17 + ord(name)) for name, cfg in CONFIGS.items()}
+    # B's heads are wide: with the other models' sharpening its scores reach the hundreds, where the rounding of one
+    # 16-bit key decides which token a query reads, in the plain implementation as in the engine
+    return {name: random_weights(cfg, 17 + ord(name), sharp=1.25 if name == "B" else 2.0) for name, cfg in CONFIGS.items()}
 
 
 @pytest.fixture(scope="module")
@@ -109,7 +111,8 @@ def _paged(rows, n_kv, D, dtype, ring_rows=0, pages_total=24, seed=0):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H, G, D, seen, sink", [(3, 3, 8, -5, True), (6, 3, 24, -33, True), (4, 2, 64, -64, False), (2, 1, 40, 0, True),
-                                                 (5, 1, 16, 7, False), (1, 1, 8, -1, True), (32, 8, 16, -70, True)])
+                                                 (5, 1, 16, 7, False), (1, 1, 8, -1, True), (32, 8, 16, -70, True), (6, 3, 96, -33, True),
+                                                 (16, 4, 128, -100, True), (3, 1, 32, 20, False), (8, 8, 64, 0, True), (2, 2, 128, -3, True)])
 def test_scores_mixed_across_heads_in_prompts(H, G, D, seen, sink, dtype):
     from trapetum_b200.csrc import ops
     g = torch.Generator().manual_seed(H * 100 + D)
@@ -123,11 +126,12 @@ def test_scores_mixed_across_heads_in_prompts(H, G, D, seen, sink, dtype):
     for n in lens:
         starts.append(starts[-1] + n)
     token_seq = sum([[b] * n for b, n in enumerate(lens)], [])
-    got = ops.attn_mixed_prefill(dev(q.reshape(T, -1), DTYPES[dtype]), dev(k.reshape(T, -1), DTYPES[dtype]),
-                                 dev(v.reshape(T, -1), DTYPES[dtype]), i32(starts), i32(token_seq), H, G, D, dev(mix), seen, sink)
     want = torch.cat([_mixed_reference(q[a:b], k[a:b], v[a:b], mix.double(), H, G, seen, sink)
                       for a, b in zip(starts, starts[1:])])
-    near(got.view(T, H, D), want, dtype, "mixed attention, prompts", rel16=1e-2)
+    for longest in (0, max(lens)):           # without the longest sequence's length the generic kernel runs, with it the tensor cores' where they can
+        got = ops.attn_mixed_prefill(dev(q.reshape(T, -1), DTYPES[dtype]), dev(k.reshape(T, -1), DTYPES[dtype]),
+                                     dev(v.reshape(T, -1), DTYPES[dtype]), i32(starts), i32(token_seq), H, G, D, dev(mix), seen, sink, longest)
+        near(got.view(T, H, D), want, dtype, f"mixed attention, prompts ({longest})", rel16=1.5e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -14,7 +14,11 @@
 // softmax and adds p.v with a slice of the head's dims per lane.  Dot products, mixing, softmax and the weighted sum
 // are 32-bit for both dtypes.
 //
-//   tb_attn_mixed_prefill   queries and keys are the step's own packed tokens
+//   tb_attn_mixed_prefill   queries and keys are the step's own packed tokens; in bfloat16 with up to 16 heads of 32, 64,
+//                           96 or 128 numbers the dot products run on tensor cores (mma.sync): a CTA takes 16 queries
+//                           of all heads, a warp a head; raw scores of 32 keys go through shared memory, every
+//                           warp mixes its own head's in 32-bit, keeps the running softmax in registers and multiplies
+//                           the rounded weights with the values
 //   tb_attn_mixed_decode    one query per sequence, keys from the paged cache (a ring if ring_rows > 0), the key range
 //                           cut into pieces; partial (max, sum, o) per piece are folded in piece order
 #include "common.cuh"
@@ -31,6 +35,7 @@ struct MixedAttnArgs {
     const float* mix;                                     // [H][H]
     float* partial;                                       // decode: [batch][H][pieces][D + 2] when pieces > 1
     int H, G, D, n_tokens, window, unit_sink, n_pieces;
+    int batch, max_seq_len;                               // prefill on tensor cores: sequences of the step, the longest's tokens
 };
 
 template <int NC>
@@ -147,14 +152,27 @@ __global__ void attn_mixed_prefill_kernel(MixedAttnArgs a) {
     }
 }
 
-template <typename T, int NC>
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;                        // 0: sixteen zero bytes
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n) : "memory");
+}
+
+// The keys and values of 32 rows for all kv heads at once: rows of D numbers padded by 16 bytes, [K | V][G][32][pitch].
+template <typename T>
+__host__ __device__ constexpr int tile_pitch(int D) { return D + 16 / (int)sizeof(T); }
+
+// STAGED: a tile of 32 cached rows of every kv head is copied into shared memory (16 bytes a thread and copy, the
+// next tile on its way while this one is used), so that the rows are fetched once for all heads and with whole
+// lines; else every lane reads its key's row from the cache itself (any size and alignment).
+template <typename T, int NC, bool STAGED>
 __global__ void attn_mixed_decode_kernel(MixedAttnArgs a) {
     pdl_launch_dependents();
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     const int H = a.H, D = a.D;
     float* q_s = smem;
     float* mix_s = q_s + H * D;
     float* raw = mix_s + H * H;
+    T* tiles = (T*)(((uintptr_t)(raw + 2 * H * 32) + 15) & ~(uintptr_t)15);      // [2 stages][K | V][G][32][pitch]
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.x, piece = blockIdx.y;
     const int kvh = h / (H / a.G);
@@ -173,6 +191,34 @@ __global__ void attn_mixed_decode_kernel(MixedAttnArgs a) {
     const int* pt = a.page_table + (size_t)b * a.pt_stride;
     MixAcc<NC> acc; acc.init();
     int buf = 0;
+    if (STAGED) {
+        const int pitch = tile_pitch<T>(D), per_row = D * (int)sizeof(T) / 16;
+        const size_t stage = (size_t)2 * a.G * 32 * pitch;
+        auto load = [&](int st, int j0) {
+            T* dst = tiles + st * stage;
+            for (int c = threadIdx.x; c < 2 * a.G * 32 * per_row; c += blockDim.x) {
+                const int ch = c % per_row, row = (c / per_row) % 32, g = (c / per_row / 32) % a.G, kv = c / per_row / 32 / a.G;
+                const int j = j0 + row;
+                const bool ok = j < end;
+                const int r = ok ? (a.ring_rows > 0 ? j % a.ring_rows : j) : 0;
+                const size_t off = (((size_t)pt[r / a.page_rows] * a.G + g) * a.page_rows + (r % a.page_rows)) * D;
+                cp_async16(dst + ((size_t)(kv * a.G + g) * 32 + row) * pitch + ch * (16 / sizeof(T)),
+                           (const T*)(kv ? a.v : a.k) + off + ch * (16 / sizeof(T)), ok);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        if (beg < end) load(0, beg);
+        int st = 0;
+        for (int j0 = beg; j0 < end; j0 += 32, buf ^= 1, st ^= 1) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();                             // the tile is there, and nobody reads the other stage any more
+            if (j0 + 32 < end) load(st ^ 1, j0 + 32);
+            const bool valid = j0 + lane < end;
+            const T* krow = tiles + st * stage + ((size_t)kvh * 32 + lane) * pitch;
+            const T* vrow = krow + (size_t)a.G * 32 * pitch;
+            mixed_chunk<T, NC>(acc, q_s + h * D, mix_s + h * H, raw + buf * H * 32, H, h, krow, vrow, valid, D, true, lane);
+        }
+    } else
     for (int j0 = beg; j0 < end; j0 += 32, buf ^= 1) {
         const int j = j0 + lane;
         const bool valid = j < end;
@@ -227,6 +273,180 @@ __global__ void attn_mixed_fold_kernel(MixedAttnArgs a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Prompts on tensor cores (bfloat16; H <= 16 heads; D = 16 KT).  16 queries a CTA, a warp a head, 32 keys a round.
+// ---------------------------------------------------------------------------
+constexpr int MP_BM = 16, MP_BN = 32, MP_RP = 40;        // raw scores' row pitch: 8 mod 32 words keeps a warp's 8-byte accesses apart
+
+__device__ __forceinline__ void mp_ldsm2(uint32_t addr, uint32_t& r0, uint32_t& r1) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ void mp_ldsm4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void mp_mma(float* d, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t mp_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *(uint32_t*)&v;
+}
+
+template <int KT>
+__global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnArgs a) {
+    pdl_launch_dependents();
+    constexpr int D = 16 * KT, PITCH = D + 8;
+    extern __shared__ __align__(16) unsigned char sm[];
+    const int H = a.H, G = a.G;
+    float* mix_s = (float*)sm;                                        // [H][H]
+    float* raw = mix_s + ((H * H + 3) & ~3);                          // [H][16][MP_RP]
+    bf16* k_s = (bf16*)(raw + H * MP_BM * MP_RP);                     // [G][32][PITCH]
+    bf16* v_s = k_s + (size_t)G * MP_BN * PITCH;                      // [G][32][PITCH]
+    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int r = lane >> 2, c = (lane & 3) * 2;                      // this thread's rows r and r + 8, columns c and c + 1 of a tile of 8
+    const int kvh = h / (H / G);
+    for (int e = threadIdx.x; e < H * H; e += blockDim.x) mix_s[e] = a.mix[e];
+    pdl_wait();
+    const int b = blockIdx.y;
+    const int s0 = a.seq_start[b], len = a.seq_start[b + 1] - s0;
+    const int i0 = blockIdx.x * MP_BM;
+    if (i0 >= len) return;
+    const int i_last = min(i0 + MP_BM - 1, len - 1);
+    const int ia = i0 + r, ib = i0 + r + 8;                           // the two queries whose scores this thread holds
+    // the queries of this head as the products' left operand, kept in registers
+    uint32_t qf[KT][4];
+    {
+        const bf16* qa = (const bf16*)a.q + (size_t)(s0 + ia) * a.q_stride + (size_t)h * D + c;
+        const bf16* qb = (const bf16*)a.q + (size_t)(s0 + ib) * a.q_stride + (size_t)h * D + c;
+#pragma unroll
+        for (int k = 0; k < KT; k++) {
+            qf[k][0] = ia < len ? *(const uint32_t*)(qa + k * 16) : 0u;
+            qf[k][1] = ib < len ? *(const uint32_t*)(qb + k * 16) : 0u;
+            qf[k][2] = ia < len ? *(const uint32_t*)(qa + k * 16 + 8) : 0u;
+            qf[k][3] = ib < len ? *(const uint32_t*)(qb + k * 16 + 8) : 0u;
+        }
+    }
+    float o[2 * KT][4];
+#pragma unroll
+    for (int n = 0; n < 2 * KT; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;     // l: this thread's share, summed over the four at the end
+    const int lo_a = first_seen(a.window, ia), lo_b = first_seen(a.window, ib);
+    const float* mix_row = mix_s + h * H;
+    constexpr int PER_ROW = D / 8;                                    // 16-byte pieces of a row
+    const uint32_t k_base = (uint32_t)__cvta_generic_to_shared(k_s + (size_t)kvh * MP_BN * PITCH);
+    const uint32_t v_base = (uint32_t)__cvta_generic_to_shared(v_s + (size_t)kvh * MP_BN * PITCH);
+    for (int j0 = first_seen(a.window, i0); j0 <= i_last; j0 += MP_BN) {
+        __syncthreads();                                              // the round before has read its tiles and raw scores
+        for (int p = threadIdx.x; p < 2 * G * MP_BN * PER_ROW; p += blockDim.x) {
+            const int ch = p % PER_ROW, row = (p / PER_ROW) % MP_BN, g = (p / PER_ROW / MP_BN) % G, kv = p / PER_ROW / MP_BN / G;
+            const bool ok = j0 + row <= i_last;
+            const bf16* src = (const bf16*)(kv ? a.v : a.k) + (size_t)(s0 + (ok ? j0 + row : 0)) * a.kv_stride + (size_t)g * D + ch * 8;
+            cp_async16((kv ? v_s : k_s) + ((size_t)g * MP_BN + row) * PITCH + ch * 8, src, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        // ---- raw scores of this head: 16 queries x 32 keys
+        float sc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+            const uint32_t ka = k_base + (uint32_t)(((nt * 8 + (lane & 7)) * PITCH + ((lane >> 3) & 1) * 8) * 2);
+#pragma unroll
+            for (int ks = 0; ks < KT; ks++) {
+                uint32_t b0, b1;
+                mp_ldsm2(ka + ks * 32, b0, b1);
+                mp_mma(sc[nt], qf[ks], b0, b1);
+            }
+            float* ra = raw + ((size_t)h * MP_BM + r) * MP_RP + nt * 8 + c;
+            *(float2*)ra = make_float2(sc[nt][0], sc[nt][1]);
+            *(float2*)(ra + 8 * MP_RP) = make_float2(sc[nt][2], sc[nt][3]);
+        }
+        __syncthreads();
+        // ---- this head's mixed scores, 32-bit
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+        for (int g = 0; g < H; g++) {
+            const float w = mix_row[g];
+            const float* ra = raw + ((size_t)g * MP_BM + r) * MP_RP + c;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const float2 x = *(const float2*)(ra + nt * 8), y = *(const float2*)(ra + nt * 8 + 8 * MP_RP);
+                sc[nt][0] = fmaf(w, x.x, sc[nt][0]); sc[nt][1] = fmaf(w, x.y, sc[nt][1]);
+                sc[nt][2] = fmaf(w, y.x, sc[nt][2]); sc[nt][3] = fmaf(w, y.y, sc[nt][3]);
+            }
+        }
+        // ---- who sees whom, and the running softmax of the two rows
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+            for (int e = 0; e < 2; e++) {
+                const int j = j0 + nt * 8 + c + e;
+                if (!(j <= ia && j >= lo_a)) sc[nt][e] = -INFINITY;
+                if (!(j <= ib && j >= lo_b)) sc[nt][2 + e] = -INFINITY;
+                mx_a = fmaxf(mx_a, sc[nt][e]); mx_b = fmaxf(mx_b, sc[nt][2 + e]);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1)); mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1)); mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float ref_a = mn_a == -INFINITY ? 0.f : mn_a, ref_b = mn_b == -INFINITY ? 0.f : mn_b;
+        const float corr_a = m_a == -INFINITY ? 0.f : expf(m_a - ref_a), corr_b = m_b == -INFINITY ? 0.f : expf(m_b - ref_b);
+        m_a = mn_a; m_b = mn_b;
+        uint32_t pa[2][4];
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const float p0 = expf(sc[nt][0] - ref_a), p1 = expf(sc[nt][1] - ref_a);      // exp(-inf) = 0 for what is not seen
+            const float p2 = expf(sc[nt][2] - ref_b), p3 = expf(sc[nt][3] - ref_b);
+            sum_a += p0 + p1; sum_b += p2 + p3;
+            pa[nt >> 1][(nt & 1) * 2] = mp_pack(p0, p1);
+            pa[nt >> 1][(nt & 1) * 2 + 1] = mp_pack(p2, p3);
+        }
+        l_a = l_a * corr_a + sum_a; l_b = l_b * corr_b + sum_b;
+        // ---- O = O * corr + P V
+#pragma unroll
+        for (int dn = 0; dn < KT; dn++) {
+            float* oa = o[2 * dn]; float* ob = o[2 * dn + 1];
+            oa[0] *= corr_a; oa[1] *= corr_a; oa[2] *= corr_b; oa[3] *= corr_b;
+            ob[0] *= corr_a; ob[1] *= corr_a; ob[2] *= corr_b; ob[3] *= corr_b;
+#pragma unroll
+            for (int kk = 0; kk < 2; kk++) {
+                uint32_t b0, b1, b2, b3;
+                mp_ldsm4_t(v_base + (uint32_t)(((kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PITCH + dn * 16 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
+                mp_mma(oa, pa[kk], b0, b1);
+                mp_mma(ob, pa[kk], b2, b3);
+            }
+        }
+    }
+    l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+    l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
+    if (a.unit_sink) {
+        // the denominator also holds exp(0); the sums stand relative to the rows' maxima
+        const float Ma = fmaxf(m_a, 0.f), Mb = fmaxf(m_b, 0.f);
+        const float fa = expf(m_a - Ma), fb = expf(m_b - Mb);
+        inv_a = fa / (l_a * fa + expf(-Ma)); inv_b = fb / (l_b * fb + expf(-Mb));
+    }
+    bf16* oa_row = (bf16*)a.out + (size_t)(s0 + ia) * a.out_stride + (size_t)h * D + c;
+    bf16* ob_row = (bf16*)a.out + (size_t)(s0 + ib) * a.out_stride + (size_t)h * D + c;
+#pragma unroll
+    for (int n = 0; n < 2 * KT; n++) {
+        if (ia < len) *(uint32_t*)(oa_row + n * 8) = mp_pack(o[n][0] * inv_a, o[n][1] * inv_a);
+        if (ib < len) *(uint32_t*)(ob_row + n * 8) = mp_pack(o[n][2] * inv_b, o[n][3] * inv_b);
+    }
+}
+
+// Whether the tensor-core form takes a step's shapes (the generic kernel takes the rest).
+extern "C" int tb_attn_mixed_prefill_mma_takes(int dtype, int H, int G, int D) {
+    if (dtype != TB_BF16 || H < 1 || H > 16 || G < 1 || H % G || D % 32 || D < 32 || D > 128) return 0;
+    const size_t smem = (size_t)((H * H + 3) & ~3) * 4 + (size_t)H * MP_BM * MP_RP * 4 + (size_t)2 * G * MP_BN * (D + 8) * 2;
+    return smem <= 200 * 1024;
+}
+
 static int pick_nc(int D) {
     const int need = (D + 31) / 32;
     int nc = 1;
@@ -248,7 +468,7 @@ static int check_shape(const MixedAttnArgs& a, size_t* smem) {
     if (a.H > 32) return tb_refuse("attn_mixed: %d heads are more than the 32 that one CTA mixes", a.H);
     if (a.D <= 0 || a.D > 512) return tb_refuse("attn_mixed: head size %d is outside [1, 512]", a.D);
     if (a.mix == nullptr) return tb_refuse("attn_mixed: no mixing matrix");
-    *smem = ((size_t)a.H * a.D + (size_t)a.H * a.H + 2 * (size_t)a.H * 32) * sizeof(float);
+    *smem = (((size_t)a.H * a.D + (size_t)a.H * a.H + 2 * (size_t)a.H * 32) * sizeof(float) + 15) / 16 * 16;
     if (*smem > 200 * 1024) return tb_refuse("attn_mixed: %d heads of %d numbers do not fit a CTA's shared memory", a.H, a.D);
     return 0;
 }
@@ -263,6 +483,17 @@ extern "C" int tb_attn_mixed_prefill(const MixedAttnArgs* args, int dtype, cudaS
     if (a.n_tokens <= 0) return 0;
     size_t smem = 0;
     if (check_shape(a, &smem)) return -1;
+    const bool aligned = (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out) & 15) == 0 && a.q_stride % 8 == 0
+        && a.kv_stride % 8 == 0 && a.out_stride % 8 == 0;
+    if (a.batch > 0 && a.max_seq_len > 0 && aligned && tb_attn_mixed_prefill_mma_takes(dtype, a.H, a.G, a.D)) {
+        const size_t sm = (size_t)((a.H * a.H + 3) & ~3) * 4 + (size_t)a.H * MP_BM * MP_RP * 4 + (size_t)2 * a.G * MP_BN * (a.D + 8) * 2;
+        dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM, a.batch);
+#define TB_MP_LAUNCH(KT) do { allow_smem(attn_mixed_prefill_mma_kernel<KT>, sm); \
+        tb_launch(attn_mixed_prefill_mma_kernel<KT>, grid, dim3(a.H * 32), sm, stream, a); } while (0)
+        switch (a.D / 16) { case 2: TB_MP_LAUNCH(2); break; case 4: TB_MP_LAUNCH(4); break; case 6: TB_MP_LAUNCH(6); break; default: TB_MP_LAUNCH(8); break; }
+#undef TB_MP_LAUNCH
+        return tb_launch_status();
+    }
     const int nc = pick_nc(a.D);
     TB_DISPATCH_1(dtype, T, MIX_DISPATCH_NC(nc,
         allow_smem(attn_mixed_prefill_kernel<T, NC>, smem);
@@ -282,9 +513,19 @@ extern "C" int tb_attn_mixed_decode(const MixedAttnArgs* args, int dtype, cudaSt
     if (a.ring_rows > 0 && (a.window == 0 || abs(a.window) > a.ring_rows))
         return tb_refuse("attn_mixed: a ring of %d rows cannot hold a window of %d", a.ring_rows, abs(a.window));
     const int nc = pick_nc(a.D);
+    // the staged form: rows of whole 16-byte pieces, two stages of every kv head's keys and values within a CTA's memory
+    const size_t el = dtype == TB_BF16 ? 2 : 4;
+    const size_t tiles = (size_t)2 * 2 * a.G * 32 * (a.D + 16 / el) * el;
+    const bool staged = (a.D * el) % 16 == 0 && (((uintptr_t)a.k | (uintptr_t)a.v) & 15) == 0 && smem + tiles <= 160 * 1024;
+    if (staged) {
+        smem += tiles;
+        TB_DISPATCH_1(dtype, T, MIX_DISPATCH_NC(nc,
+            allow_smem(attn_mixed_decode_kernel<T, NC, true>, smem);
+            tb_launch(attn_mixed_decode_kernel<T, NC, true>, dim3(a.n_tokens, a.n_pieces), dim3(a.H * 32), smem, stream, a)));
+    } else
     TB_DISPATCH_1(dtype, T, MIX_DISPATCH_NC(nc,
-        allow_smem(attn_mixed_decode_kernel<T, NC>, smem);
-        tb_launch(attn_mixed_decode_kernel<T, NC>, dim3(a.n_tokens, a.n_pieces), dim3(a.H * 32), smem, stream, a)));
+        allow_smem(attn_mixed_decode_kernel<T, NC, false>, smem);
+        tb_launch(attn_mixed_decode_kernel<T, NC, false>, dim3(a.n_tokens, a.n_pieces), dim3(a.H * 32), smem, stream, a)));
     int st = tb_launch_status();
     if (st || a.n_pieces == 1) return st;
     TB_DISPATCH_1(dtype, T, tb_launch(attn_mixed_fold_kernel<T>, dim3(a.n_tokens, a.H), dim3(128), 0, stream, a));

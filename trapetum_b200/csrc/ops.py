@@ -1574,7 +1574,17 @@ class _MixedAttnArgs(ctypes.Structure):
                 ("seq_start", c_void_p), ("token_seq", c_void_p), ("page_table", c_void_p), ("pt_stride", c_int),
                 ("page_rows", c_int), ("ring_rows", c_int), ("len_after", c_void_p), ("out", c_void_p),
                 ("out_stride", c_longlong), ("mix", c_void_p), ("partial", c_void_p), ("H", c_int), ("G", c_int), ("D", c_int),
-                ("n_tokens", c_int), ("window", c_int), ("unit_sink", c_int), ("n_pieces", c_int)]
+                ("n_tokens", c_int), ("window", c_int), ("unit_sink", c_int), ("n_pieces", c_int), ("batch", c_int),
+                ("max_seq_len", c_int)]
+
+
+def attn_mixed_padded_head(dtype: torch.dtype, n_heads: int, n: int) -> int:
+    """The head size at which a mixer whose scores are mixed across heads stores keys and values of up to ``n`` numbers
+    a head: in bfloat16 with up to 16 heads the next of 32, 64, 96, 128 (what the tensor-core form of its prefill
+    kernel takes), else the next multiple of 8 (the generic kernels take any size; rows of whole 16-byte pieces)."""
+    if dtype == torch.bfloat16 and n_heads <= 16 and n <= 128:
+        return (n + 31) // 32 * 32
+    return (n + 7) // 8 * 8
 
 
 def _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink):
@@ -1593,11 +1603,12 @@ def _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink):
 
 def attn_mixed_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_start: torch.Tensor, token_seq: torch.Tensor,
                        n_heads: int, n_kv_heads: int, head_dim: int, mix: torch.Tensor, window: int,
-                       unit_sink: bool) -> torch.Tensor:
+                       unit_sink: bool, max_seq_len: int = 0) -> torch.Tensor:
     """Causal attention of packed sequences whose scores are mixed across heads before the softmax:
     ``s_h = sum_g mix[h, g] (q_g . k)`` (``mix`` float32 [H, H]; the caller folds the scale in).  ``window`` W > 0: the
     last W positions are seen; -C: the positions of the query's own block of C, blocks counted from position 0; 0: all
-    earlier ones.  ``unit_sink``: the softmax denominator also holds exp(0)."""
+    earlier ones.  ``unit_sink``: the softmax denominator also holds exp(0).  ``max_seq_len``: the longest sequence
+    of the step; with it the tensor-core form runs where it takes the shapes (it sizes that form's grid)."""
     _cuda(q, k, v, seq_start, token_seq, mix)
     for name, t in (("k", k), ("v", v)):
         _rows_contig(t, "attn_mixed: " + name)
@@ -1606,6 +1617,7 @@ def attn_mixed_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_st
     a, out = _mixed_args(q, n_heads, n_kv_heads, head_dim, mix, window, unit_sink)
     a.k = k.data_ptr(); a.v = v.data_ptr(); a.kv_stride = k.stride(0)
     a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr()
+    a.batch = seq_start.numel() - 1; a.max_seq_len = int(max_seq_len)
     lib = build.load("attention_mixed")
     _check(lib, lib.tb_attn_mixed_prefill(ctypes.byref(a), c_int(code(q.dtype)), _stream()), "attn_mixed_prefill")
     return out

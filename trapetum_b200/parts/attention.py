@@ -138,7 +138,8 @@ class Attention(Mixer):
                 raise ValueError("attention: 'proj_norm', 'head_temp', 'value_dim' and 'out_gate' go with a rotate-half "
                                  "rotation or with no position encoding")
             # the mixing kernels take any head size; the tensor-core kernels want one of theirs
-            self.pad = (max(self.hd, self.vd) + 7) // 8 * 8 if self.mixed else ops.attn_padded_head(rt.dtype, max(self.hd, self.vd))
+            self.pad = ops.attn_mixed_padded_head(rt.dtype, self.n_heads, max(self.hd, self.vd)) if self.mixed \
+                else ops.attn_padded_head(rt.dtype, max(self.hd, self.vd))
         self.wq_norm = self.wk_norm = self.head_temp = self.w_o_padded = self.mix = self.b_proj = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
@@ -356,7 +357,8 @@ class Attention(Mixer):
         if self.mixed:
             seen = -self.block if self.block else (self.window or 0)
             if ctx.is_prefill:
-                o = ops.attn_mixed_prefill(q, k, v, ctx.seq_start, ctx.token_seq, H, G, D, self.mix, seen, self.unit_sink)
+                o = ops.attn_mixed_prefill(q, k, v, ctx.seq_start, ctx.token_seq, H, G, D, self.mix, seen, self.unit_sink,
+                                           ctx.max_seq_len)
             else:
                 o = ops.attn_mixed_decode(q, line.k, line.v, line.page_table, ctx.len_after, H, G, D, self.mix, seen,
                                           self.unit_sink, line.ring_rows, ctx.len_bucket)

@@ -46,6 +46,15 @@ class RMSNorm(Norm):
         """``h += scale * (sum of the branch outputs)`` in place, returns ``norm(h)``; one kernel."""
         return ops.add_scaled_rmsnorm(h, branches, scale, self.weight, self.eps, self.offset, out_dtype)
 
+    def add_apply(self, h: torch.Tensor, a: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """``h += a`` in place (a branch output that no norm follows), returns ``norm(h)``; one kernel where the branch
+        output is 32-bit (a matrix or split-K partial sums)."""
+        if a.dtype == torch.float32:
+            return ops.add_scaled_rmsnorm(h, [a if a.dim() == 3 else a.contiguous()], 1.0, self.weight, self.eps, self.offset,
+                                          out_dtype)
+        ops.residual_add(h, a)
+        return self.apply(h, out_dtype)
+
     def kernel_files(self):
         return ("norm",)
 
