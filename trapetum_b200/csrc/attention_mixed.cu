@@ -60,8 +60,11 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q_s, const T*
         for (int e = 0; e < D; e += N) {
             const uint4 u = *(const uint4*)(krow + e);
             const T* x = (const T*)&u;
+            __align__(16) float qv[N];                                 // the query from shared memory 16 bytes at a time (every lane the same)
 #pragma unroll
-            for (int i = 0; i < N; i++) d = fmaf(q_s[e + i], to_f<T>(x[i]), d);
+            for (int i = 0; i < N; i += 4) *(float4*)(qv + i) = *(const float4*)(q_s + e + i);
+#pragma unroll
+            for (int i = 0; i < N; i++) d = fmaf(qv[i], to_f<T>(x[i]), d);
         }
     } else {
         for (int e = 0; e < D; e++) d = fmaf(q_s[e], to_f<T>(krow[e]), d);
@@ -89,15 +92,33 @@ __device__ __forceinline__ void mixed_chunk(MixAcc<NC>& acc, const float* q_s, c
     acc.m = m_new;
 #pragma unroll
     for (int c = 0; c < NC; c++) acc.o[c] *= corr;
+    // a lane owns the NC consecutive dims from lane * NC on; with whole 16-byte rows it reads them in one piece
+    constexpr int BYTES = NC * (int)sizeof(T);
+    const bool wide = vec && (D % NC) == 0 && (BYTES == 4 || BYTES == 8 || BYTES % 16 == 0);
+    const int d0 = lane * NC;
     for (int jj = 0; jj < 32; jj++) {
         const float pj = __shfl_sync(0xffffffffu, p, jj);
         const unsigned long long vp = __shfl_sync(0xffffffffu, (unsigned long long)(uintptr_t)vrow, jj);
         if (pj == 0.f) continue;
         const T* v = (const T*)(uintptr_t)vp;
+        if (wide) {
+            if (d0 < D) {
+                __align__(16) T x[NC];
+                if (BYTES == 4) *(uint32_t*)x = *(const uint32_t*)(v + d0);
+                else if (BYTES == 8) *(uint2*)x = *(const uint2*)(v + d0);
+                else {
 #pragma unroll
-        for (int c = 0; c < NC; c++) {
-            const int d = lane + 32 * c;
-            if (d < D) acc.o[c] = fmaf(pj, to_f<T>(v[d]), acc.o[c]);
+                    for (int i = 0; i < BYTES / 16; i++) ((uint4*)x)[i] = ((const uint4*)(v + d0))[i];
+                }
+#pragma unroll
+                for (int c = 0; c < NC; c++) acc.o[c] = fmaf(pj, to_f<T>(x[c]), acc.o[c]);
+            }
+        } else {
+#pragma unroll
+            for (int c = 0; c < NC; c++) {
+                const int d = d0 + c;
+                if (d < D) acc.o[c] = fmaf(pj, to_f<T>(v[d]), acc.o[c]);
+            }
         }
     }
 }
@@ -147,7 +168,7 @@ __global__ void attn_mixed_prefill_kernel(MixedAttnArgs a) {
     T* orow = (T*)a.out + (size_t)t * a.out_stride + (size_t)h * D;
 #pragma unroll
     for (int c = 0; c < NC; c++) {
-        const int d = lane + 32 * c;
+        const int d = lane * NC + c;
         if (d < D) orow[d] = from_f<T>(acc.o[c] * inv);
     }
 }
@@ -239,11 +260,11 @@ __global__ void attn_mixed_decode_kernel(MixedAttnArgs a) {
         }
         T* orow = (T*)a.out + (size_t)b * a.out_stride + (size_t)h * D;
 #pragma unroll
-        for (int c = 0; c < NC; c++) { const int d = lane + 32 * c; if (d < D) orow[d] = from_f<T>(acc.o[c] * inv); }
+        for (int c = 0; c < NC; c++) { const int d = lane * NC + c; if (d < D) orow[d] = from_f<T>(acc.o[c] * inv); }
     } else {
         float* p = a.partial + (((size_t)b * H + h) * a.n_pieces + piece) * (D + 2);
 #pragma unroll
-        for (int c = 0; c < NC; c++) { const int d = lane + 32 * c; if (d < D) p[d] = acc.o[c]; }
+        for (int c = 0; c < NC; c++) { const int d = lane * NC + c; if (d < D) p[d] = acc.o[c]; }
         if (lane == 0) { p[D] = acc.m; p[D + 1] = acc.l; }
     }
 }
@@ -302,8 +323,8 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
     const int H = a.H, G = a.G;
     float* mix_s = (float*)sm;                                        // [H][H]
     float* raw = mix_s + ((H * H + 3) & ~3);                          // [H][16][MP_RP]
-    bf16* k_s = (bf16*)(raw + H * MP_BM * MP_RP);                     // [G][32][PITCH]
-    bf16* v_s = k_s + (size_t)G * MP_BN * PITCH;                      // [G][32][PITCH]
+    bf16* tiles = (bf16*)(raw + H * MP_BM * MP_RP);                   // [2 stages][K | V][G][32][PITCH]
+    const size_t half_stage = (size_t)G * MP_BN * PITCH, stage = 2 * half_stage;
     const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = lane >> 2, c = (lane & 3) * 2;                      // this thread's rows r and r + 8, columns c and c + 1 of a tile of 8
     const int kvh = h / (H / G);
@@ -335,19 +356,26 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
     const int lo_a = first_seen(a.window, ia), lo_b = first_seen(a.window, ib);
     const float* mix_row = mix_s + h * H;
     constexpr int PER_ROW = D / 8;                                    // 16-byte pieces of a row
-    const uint32_t k_base = (uint32_t)__cvta_generic_to_shared(k_s + (size_t)kvh * MP_BN * PITCH);
-    const uint32_t v_base = (uint32_t)__cvta_generic_to_shared(v_s + (size_t)kvh * MP_BN * PITCH);
-    for (int j0 = first_seen(a.window, i0); j0 <= i_last; j0 += MP_BN) {
-        __syncthreads();                                              // the round before has read its tiles and raw scores
+    // keys and values of 32 positions for every kv head; the next round's are on their way while this round computes
+    auto load = [&](int st, int j0) {
+        bf16* dst = tiles + st * stage;
         for (int p = threadIdx.x; p < 2 * G * MP_BN * PER_ROW; p += blockDim.x) {
             const int ch = p % PER_ROW, row = (p / PER_ROW) % MP_BN, g = (p / PER_ROW / MP_BN) % G, kv = p / PER_ROW / MP_BN / G;
             const bool ok = j0 + row <= i_last;
             const bf16* src = (const bf16*)(kv ? a.v : a.k) + (size_t)(s0 + (ok ? j0 + row : 0)) * a.kv_stride + (size_t)g * D + ch * 8;
-            cp_async16((kv ? v_s : k_s) + ((size_t)g * MP_BN + row) * PITCH + ch * 8, src, ok);
+            cp_async16(dst + kv * half_stage + ((size_t)g * MP_BN + row) * PITCH + ch * 8, src, ok);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int j_first = first_seen(a.window, i0);
+    load(0, j_first);
+    int st = 0;
+    for (int j0 = j_first; j0 <= i_last; j0 += MP_BN, st ^= 1) {
         asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
+        __syncthreads();                                              // this round's tiles are there; the round before has read its own and the raw scores
+        if (j0 + MP_BN <= i_last) load(st ^ 1, j0 + MP_BN);
+        const uint32_t k_base = (uint32_t)__cvta_generic_to_shared(tiles + st * stage + (size_t)kvh * MP_BN * PITCH);
+        const uint32_t v_base = k_base + (uint32_t)(half_stage * 2);
         // ---- raw scores of this head: 16 queries x 32 keys
         float sc[4][4];
 #pragma unroll
@@ -443,7 +471,7 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
 // Whether the tensor-core form takes a step's shapes (the generic kernel takes the rest).
 extern "C" int tb_attn_mixed_prefill_mma_takes(int dtype, int H, int G, int D) {
     if (dtype != TB_BF16 || H < 1 || H > 16 || G < 1 || H % G || D % 32 || D < 32 || D > 128) return 0;
-    const size_t smem = (size_t)((H * H + 3) & ~3) * 4 + (size_t)H * MP_BM * MP_RP * 4 + (size_t)2 * G * MP_BN * (D + 8) * 2;
+    const size_t smem = (size_t)((H * H + 3) & ~3) * 4 + (size_t)H * MP_BM * MP_RP * 4 + (size_t)2 * 2 * G * MP_BN * (D + 8) * 2;
     return smem <= 200 * 1024;
 }
 
@@ -486,7 +514,7 @@ extern "C" int tb_attn_mixed_prefill(const MixedAttnArgs* args, int dtype, cudaS
     const bool aligned = (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out) & 15) == 0 && a.q_stride % 8 == 0
         && a.kv_stride % 8 == 0 && a.out_stride % 8 == 0;
     if (a.batch > 0 && a.max_seq_len > 0 && aligned && tb_attn_mixed_prefill_mma_takes(dtype, a.H, a.G, a.D)) {
-        const size_t sm = (size_t)((a.H * a.H + 3) & ~3) * 4 + (size_t)a.H * MP_BM * MP_RP * 4 + (size_t)2 * a.G * MP_BN * (a.D + 8) * 2;
+        const size_t sm = (size_t)((a.H * a.H + 3) & ~3) * 4 + (size_t)a.H * MP_BM * MP_RP * 4 + (size_t)2 * 2 * a.G * MP_BN * (a.D + 8) * 2;
         dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM, a.batch);
 #define TB_MP_LAUNCH(KT) do { allow_smem(attn_mixed_prefill_mma_kernel<KT>, sm); \
         tb_launch(attn_mixed_prefill_mma_kernel<KT>, grid, dim3(a.H * 32), sm, stream, a); } while (0)
