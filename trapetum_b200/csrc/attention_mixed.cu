@@ -57,15 +57,17 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ q_s, const T*
     float d = 0.f;
     constexpr int N = Vec<T>::N;
     if (vec) {
+        float d4[4] = {0.f, 0.f, 0.f, 0.f};              // four sums side by side: no product waits for the one before it
         for (int e = 0; e < D; e += N) {
             const uint4 u = *(const uint4*)(krow + e);
             const T* x = (const T*)&u;
-            __align__(16) float qv[N];                                 // the query from shared memory 16 bytes at a time (every lane the same)
+            __align__(16) float qv[N];                   // the query from shared memory 16 bytes at a time (every lane the same)
 #pragma unroll
             for (int i = 0; i < N; i += 4) *(float4*)(qv + i) = *(const float4*)(q_s + e + i);
 #pragma unroll
-            for (int i = 0; i < N; i++) d = fmaf(qv[i], to_f<T>(x[i]), d);
+            for (int i = 0; i < N; i++) d4[i & 3] = fmaf(qv[i], to_f<T>(x[i]), d4[i & 3]);
         }
+        d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
     } else {
         for (int e = 0; e < D; e++) d = fmaf(q_s[e], to_f<T>(krow[e]), d);
     }
@@ -379,15 +381,19 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
         // ---- raw scores of this head: 16 queries x 32 keys
         float sc[4][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-            const uint32_t ka = k_base + (uint32_t)(((nt * 8 + (lane & 7)) * PITCH + ((lane >> 3) & 1) * 8) * 2);
+        for (int nt = 0; nt < 4; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+        const uint32_t ka = k_base + (uint32_t)((((lane & 7)) * PITCH + ((lane >> 3) & 1) * 8) * 2);
 #pragma unroll
-            for (int ks = 0; ks < KT; ks++) {
+        for (int ks = 0; ks < KT; ks++) {                              // the four tiles of 8 keys side by side: four sums in flight
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
                 uint32_t b0, b1;
-                mp_ldsm2(ka + ks * 32, b0, b1);
+                mp_ldsm2(ka + (uint32_t)(nt * 8 * PITCH * 2) + ks * 32, b0, b1);
                 mp_mma(sc[nt], qf[ks], b0, b1);
             }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
             float* ra = raw + ((size_t)h * MP_BM + r) * MP_RP + nt * 8 + c;
             *(float2*)ra = make_float2(sc[nt][0], sc[nt][1]);
             *(float2*)(ra + 8 * MP_RP) = make_float2(sc[nt][2], sc[nt][3]);
@@ -437,16 +443,15 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
         l_a = l_a * corr_a + sum_a; l_b = l_b * corr_b + sum_b;
         // ---- O = O * corr + P V
 #pragma unroll
-        for (int dn = 0; dn < KT; dn++) {
-            float* oa = o[2 * dn]; float* ob = o[2 * dn + 1];
-            oa[0] *= corr_a; oa[1] *= corr_a; oa[2] *= corr_b; oa[3] *= corr_b;
-            ob[0] *= corr_a; ob[1] *= corr_a; ob[2] *= corr_b; ob[3] *= corr_b;
+        for (int n = 0; n < 2 * KT; n++) { o[n][0] *= corr_a; o[n][1] *= corr_a; o[n][2] *= corr_b; o[n][3] *= corr_b; }
 #pragma unroll
-            for (int kk = 0; kk < 2; kk++) {
+        for (int kk = 0; kk < 2; kk++) {                               // all tiles of the values' dims side by side
+#pragma unroll
+            for (int dn = 0; dn < KT; dn++) {
                 uint32_t b0, b1, b2, b3;
                 mp_ldsm4_t(v_base + (uint32_t)(((kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PITCH + dn * 16 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
-                mp_mma(oa, pa[kk], b0, b1);
-                mp_mma(ob, pa[kk], b2, b3);
+                mp_mma(o[2 * dn], pa[kk], b0, b1);
+                mp_mma(o[2 * dn + 1], pa[kk], b2, b3);
             }
         }
     }

@@ -560,7 +560,7 @@ extern "C" int tb_fold_rmsnorm(float* h, int post, float alpha, const void* a, i
 //
 // One CTA per row, the new row kept in shared memory between the two passes when it fits.  Everything is 32-bit.
 template <typename TW, typename TO, int VEC>
-__global__ void add_scaled_rmsnorm_kernel(float* __restrict__ h, float scale, const float* __restrict__ a, int a_splits,
+__global__ void __launch_bounds__(1024) add_scaled_rmsnorm_kernel(float* __restrict__ h, float scale, const float* __restrict__ a, int a_splits,
                                           long long a_stride, const float* __restrict__ b, int b_splits, long long b_stride,
                                           const TW* __restrict__ w, float eps, float offset, TO* __restrict__ out, int width,
                                           int row_cache) {
