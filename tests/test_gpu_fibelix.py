@@ -112,7 +112,8 @@ def _paged(rows, n_kv, D, dtype, ring_rows=0, pages_total=24, seed=0):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H, G, D, seen, sink", [(3, 3, 8, -5, True), (6, 3, 24, -33, True), (4, 2, 64, -64, False), (2, 1, 40, 0, True),
                                                  (5, 1, 16, 7, False), (1, 1, 8, -1, True), (32, 8, 16, -70, True), (6, 3, 96, -33, True),
-                                                 (16, 4, 128, -100, True), (3, 1, 32, 20, False), (8, 8, 64, 0, True), (2, 2, 128, -3, True)])
+                                                 (16, 4, 128, -100, True), (3, 1, 32, 20, False), (8, 8, 64, 0, True), (2, 2, 128, -3, True),
+                                                 (32, 8, 128, -100, True), (24, 3, 64, -33, False), (20, 4, 32, 0, True), (17, 17, 32, 9, True)])
 def test_scores_mixed_across_heads_in_prompts(H, G, D, seen, sink, dtype):
     from trapetum_b200.csrc import ops
     g = torch.Generator().manual_seed(H * 100 + D)
@@ -266,9 +267,7 @@ def test_routing_by_the_largest_logits_with_a_bias(E, top):
     part = torch.zeros(2, T, 16)
     part[0, :, :E] = (z - b).float() * 0.25
     part[1, :, :E] = (z - b).float() * 0.75
-    part = dev(part)
-    ops.add_bias(part[0][:, :E], dev(b.float()))
-    gi, gw, _ = ops.moe_route(part, E, None, False, top, 1, 1, 1, 0.0, "softmax", 1.0)
+    gi, gw, _ = ops.moe_route(dev(part), E, None, False, top, 1, 1, 1, 0.0, "softmax", 1.0, dev(b.float()))
     order = torch.argsort(gi.cpu().long(), dim=1)
     want_order = torch.argsort(idx, dim=1)
     assert torch.equal(torch.gather(gi.cpu().long(), 1, order), torch.gather(idx, 1, want_order))

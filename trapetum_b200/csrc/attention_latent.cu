@@ -40,7 +40,7 @@ struct LatentRowsArgs {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(128) latent_rows_kernel(LatentRowsArgs a) {
+__global__ void __launch_bounds__(1024) latent_rows_kernel(LatentRowsArgs a) {
     pdl_launch_dependents();
     extern __shared__ float row_s[];
     __shared__ float red[33];
@@ -187,7 +187,9 @@ extern "C" int tb_latent_rows(const LatentRowsArgs* args, int dtype, cudaStream_
         return tb_refuse("latent_rows: Q=%d gate=%d need their outputs", a.Q, a.n_gate);
     if (a.ring_rows > 0 && (a.ring_rows % a.page_rows || a.len_after == nullptr))
         return tb_refuse("latent_rows: a ring of %d rows needs whole pages and the sequences' lengths", a.ring_rows);
-    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(128),
+    // few tokens (a decode step) are a chain of memory waits per thread: eight times the threads a token shorten it
+    const int threads = a.n_tokens <= 2 * 148 ? 1024 : 128;
+    TB_DISPATCH_1(dtype, T, tb_launch(latent_rows_kernel<T>, dim3(a.n_tokens), dim3(threads),
                                       (size_t)(a.C + a.R + a.Q + a.n_gate) * sizeof(float), stream, a));
     return tb_launch_status();
 }

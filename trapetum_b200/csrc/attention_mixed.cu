@@ -36,6 +36,7 @@ struct MixedAttnArgs {
     float* partial;                                       // decode: [batch][H][pieces][D + 2] when pieces > 1
     int H, G, D, n_tokens, window, unit_sink, n_pieces;
     int batch, max_seq_len;                               // prefill on tensor cores: sequences of the step, the longest's tokens
+    int stages;                                           // ... and how many rounds' keys and values lie in shared memory (set by the library)
 };
 
 template <int NC>
@@ -298,7 +299,10 @@ __global__ void attn_mixed_fold_kernel(MixedAttnArgs a) {
 
 
 // ---------------------------------------------------------------------------
-// Prompts on tensor cores (bfloat16; H <= 16 heads; D = 16 KT).  16 queries a CTA, a warp a head, 32 keys a round.
+// Prompts on tensor cores (bfloat16; H <= 32 heads; D = 16 KT).  16 queries a CTA, a warp a head, 32 keys a round.
+// With more than 16 heads two CTAs (along z) share a tile of queries: each makes the raw scores of ALL heads (a warp
+// those of heads w and w + 16; the second one's queries come from memory every round, not from registers), because
+// every head's mixed score needs them all, and mixes, weighs and writes 16 heads of its own.
 // ---------------------------------------------------------------------------
 constexpr int MP_BM = 16, MP_BN = 32, MP_RP = 40;        // raw scores' row pitch: 8 mod 32 words keeps a warp's 8-byte accesses apart
 
@@ -317,19 +321,36 @@ __device__ __forceinline__ uint32_t mp_pack(float lo, float hi) {
     return *(uint32_t*)&v;
 }
 
-template <int KT>
+// How many kv heads' values a CTA keeps: all of them with up to 16 heads, else those of 16 consecutive heads.
+__host__ __device__ inline int mp_value_heads(int H, int G) {
+    if (H <= 16) return G;
+    const int per = H / G, n = 15 / per + 2;
+    return n < G ? n : G;
+}
+__host__ inline size_t mp_smem(int H, int G, int D, int stages) {
+    return (size_t)((H * H + 3) & ~3) * 4 + (size_t)H * MP_BM * MP_RP * 4 + (size_t)stages * (G + mp_value_heads(H, G)) * MP_BN * (D + 8) * 2;
+}
+
+// MULTI: more than 16 heads (the second paragraph above); else a warp's only raw scores are its own head's.
+template <int KT, bool MULTI>
 __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnArgs a) {
     pdl_launch_dependents();
     constexpr int D = 16 * KT, PITCH = D + 8;
     extern __shared__ __align__(16) unsigned char sm[];
-    const int H = a.H, G = a.G;
+    const int H = a.H, G = a.G, GV = mp_value_heads(H, G);
     float* mix_s = (float*)sm;                                        // [H][H]
     float* raw = mix_s + ((H * H + 3) & ~3);                          // [H][16][MP_RP]
-    bf16* tiles = (bf16*)(raw + H * MP_BM * MP_RP);                   // [2 stages][K | V][G][32][PITCH]
-    const size_t half_stage = (size_t)G * MP_BN * PITCH, stage = 2 * half_stage;
-    const int h = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    bf16* tiles = (bf16*)(raw + H * MP_BM * MP_RP);                   // [stages][K: G | V: GV][32][PITCH]
+    const size_t k_part = (size_t)G * MP_BN * PITCH, stage = k_part + (size_t)GV * MP_BN * PITCH;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int h_raw = warp < H ? warp : 0;
+    const int h_out = blockIdx.z * 16 + warp;                         // the head this warp mixes, weighs and writes
+    const bool has_out = h_out < H;
+    const int h = has_out ? h_out : h_raw;                            // the head whose queries stay in registers
     const int r = lane >> 2, c = (lane & 3) * 2;                      // this thread's rows r and r + 8, columns c and c + 1 of a tile of 8
-    const int kvh = h / (H / G);
+    const int per_kv = H / G;
+    const int kv_lo = (blockIdx.z * 16) / per_kv;                     // the first kv head whose values this CTA needs
+    const int kvh = h / per_kv;
     for (int e = threadIdx.x; e < H * H; e += blockDim.x) mix_s[e] = a.mix[e];
     pdl_wait();
     const int b = blockIdx.y;
@@ -358,47 +379,64 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
     const int lo_a = first_seen(a.window, ia), lo_b = first_seen(a.window, ib);
     const float* mix_row = mix_s + h * H;
     constexpr int PER_ROW = D / 8;                                    // 16-byte pieces of a row
-    // keys and values of 32 positions for every kv head; the next round's are on their way while this round computes
+    // keys of 32 positions for every kv head and values for this CTA's; with two stages the next round's are on their
+    // way while this round computes
     auto load = [&](int st, int j0) {
         bf16* dst = tiles + st * stage;
-        for (int p = threadIdx.x; p < 2 * G * MP_BN * PER_ROW; p += blockDim.x) {
-            const int ch = p % PER_ROW, row = (p / PER_ROW) % MP_BN, g = (p / PER_ROW / MP_BN) % G, kv = p / PER_ROW / MP_BN / G;
-            const bool ok = j0 + row <= i_last;
-            const bf16* src = (const bf16*)(kv ? a.v : a.k) + (size_t)(s0 + (ok ? j0 + row : 0)) * a.kv_stride + (size_t)g * D + ch * 8;
-            cp_async16(dst + kv * half_stage + ((size_t)g * MP_BN + row) * PITCH + ch * 8, src, ok);
+        for (int p = threadIdx.x; p < (G + GV) * MP_BN * PER_ROW; p += blockDim.x) {
+            const int ch = p % PER_ROW, row = (p / PER_ROW) % MP_BN, gg = p / PER_ROW / MP_BN;
+            const bool is_v = gg >= G;
+            const int g = is_v ? kv_lo + gg - G : gg;
+            const bool ok = j0 + row <= i_last && g < G;
+            const bf16* src = (const bf16*)(is_v ? a.v : a.k) + (size_t)(s0 + (ok ? j0 + row : 0)) * a.kv_stride + (size_t)(ok ? g : 0) * D + ch * 8;
+            cp_async16(dst + ((size_t)gg * MP_BN + row) * PITCH + ch * 8, src, ok);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     const int j_first = first_seen(a.window, i0);
-    load(0, j_first);
+    const bool two = a.stages >= 2;
+    if (two) load(0, j_first);
     int st = 0;
-    for (int j0 = j_first; j0 <= i_last; j0 += MP_BN, st ^= 1) {
+    for (int j0 = j_first; j0 <= i_last; j0 += MP_BN, st ^= (two ? 1 : 0)) {
+        if (!two) { __syncthreads(); load(0, j0); }                   // one stage: the round before must have read it
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                              // this round's tiles are there; the round before has read its own and the raw scores
-        if (j0 + MP_BN <= i_last) load(st ^ 1, j0 + MP_BN);
-        const uint32_t k_base = (uint32_t)__cvta_generic_to_shared(tiles + st * stage + (size_t)kvh * MP_BN * PITCH);
-        const uint32_t v_base = k_base + (uint32_t)(half_stage * 2);
+        if (two && j0 + MP_BN <= i_last) load(st ^ 1, j0 + MP_BN);
+        const uint32_t t_base = (uint32_t)__cvta_generic_to_shared(tiles + st * stage);
+        const uint32_t v_base = t_base + (uint32_t)((k_part + (size_t)(kvh - kv_lo) * MP_BN * PITCH) * 2);
         // ---- raw scores of this head: 16 queries x 32 keys
         float sc[4][4];
+        for (int hr = warp; hr < (MULTI ? H : warp + 1); hr += 16) {  // the heads whose raw scores this warp makes
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
-        const uint32_t ka = k_base + (uint32_t)((((lane & 7)) * PITCH + ((lane >> 3) & 1) * 8) * 2);
+            for (int nt = 0; nt < 4; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+            const uint32_t ka = t_base + (uint32_t)((((size_t)(hr / per_kv) * MP_BN + (lane & 7)) * PITCH + ((lane >> 3) & 1) * 8) * 2);
+            const bool mine = !MULTI || hr == h;                       // its queries are in registers; the other head's come from memory
+            const bf16* qa = (const bf16*)a.q + (size_t)(s0 + ia) * a.q_stride + (size_t)hr * D + c;
+            const bf16* qb = (const bf16*)a.q + (size_t)(s0 + ib) * a.q_stride + (size_t)hr * D + c;
 #pragma unroll
-        for (int ks = 0; ks < KT; ks++) {                              // the four tiles of 8 keys side by side: four sums in flight
+            for (int ks = 0; ks < KT; ks++) {                          // the four tiles of 8 keys side by side: four sums in flight
+                uint32_t qq[4];
+                if (mine) { qq[0] = qf[ks][0]; qq[1] = qf[ks][1]; qq[2] = qf[ks][2]; qq[3] = qf[ks][3]; }
+                else {
+                    qq[0] = ia < len ? *(const uint32_t*)(qa + ks * 16) : 0u; qq[1] = ib < len ? *(const uint32_t*)(qb + ks * 16) : 0u;
+                    qq[2] = ia < len ? *(const uint32_t*)(qa + ks * 16 + 8) : 0u; qq[3] = ib < len ? *(const uint32_t*)(qb + ks * 16 + 8) : 0u;
+                }
+#pragma unroll
+                for (int nt = 0; nt < 4; nt++) {
+                    uint32_t b0, b1;
+                    mp_ldsm2(ka + (uint32_t)(nt * 8 * PITCH * 2) + ks * 32, b0, b1);
+                    mp_mma(sc[nt], qq, b0, b1);
+                }
+            }
 #pragma unroll
             for (int nt = 0; nt < 4; nt++) {
-                uint32_t b0, b1;
-                mp_ldsm2(ka + (uint32_t)(nt * 8 * PITCH * 2) + ks * 32, b0, b1);
-                mp_mma(sc[nt], qf[ks], b0, b1);
+                float* ra = raw + ((size_t)hr * MP_BM + r) * MP_RP + nt * 8 + c;
+                *(float2*)ra = make_float2(sc[nt][0], sc[nt][1]);
+                *(float2*)(ra + 8 * MP_RP) = make_float2(sc[nt][2], sc[nt][3]);
             }
         }
-#pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            float* ra = raw + ((size_t)h * MP_BM + r) * MP_RP + nt * 8 + c;
-            *(float2*)ra = make_float2(sc[nt][0], sc[nt][1]);
-            *(float2*)(ra + 8 * MP_RP) = make_float2(sc[nt][2], sc[nt][3]);
-        }
         __syncthreads();
+        if (MULTI && !has_out) continue;                               // a warp without a head of its own only made raw scores
         // ---- this head's mixed scores, 32-bit
 #pragma unroll
         for (int nt = 0; nt < 4; nt++) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
@@ -464,6 +502,7 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
         const float fa = expf(m_a - Ma), fb = expf(m_b - Mb);
         inv_a = fa / (l_a * fa + expf(-Ma)); inv_b = fb / (l_b * fb + expf(-Mb));
     }
+    if (!has_out) return;
     bf16* oa_row = (bf16*)a.out + (size_t)(s0 + ia) * a.out_stride + (size_t)h * D + c;
     bf16* ob_row = (bf16*)a.out + (size_t)(s0 + ib) * a.out_stride + (size_t)h * D + c;
 #pragma unroll
@@ -475,9 +514,8 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
 
 // Whether the tensor-core form takes a step's shapes (the generic kernel takes the rest).
 extern "C" int tb_attn_mixed_prefill_mma_takes(int dtype, int H, int G, int D) {
-    if (dtype != TB_BF16 || H < 1 || H > 16 || G < 1 || H % G || D % 32 || D < 32 || D > 128) return 0;
-    const size_t smem = (size_t)((H * H + 3) & ~3) * 4 + (size_t)H * MP_BM * MP_RP * 4 + (size_t)2 * 2 * G * MP_BN * (D + 8) * 2;
-    return smem <= 200 * 1024;
+    if (dtype != TB_BF16 || H < 1 || H > 32 || G < 1 || H % G || D % 32 || D < 32 || D > 128) return 0;
+    return mp_smem(H, G, D, 1) <= 200 * 1024;
 }
 
 static int pick_nc(int D) {
@@ -519,10 +557,15 @@ extern "C" int tb_attn_mixed_prefill(const MixedAttnArgs* args, int dtype, cudaS
     const bool aligned = (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v | (uintptr_t)a.out) & 15) == 0 && a.q_stride % 8 == 0
         && a.kv_stride % 8 == 0 && a.out_stride % 8 == 0;
     if (a.batch > 0 && a.max_seq_len > 0 && aligned && tb_attn_mixed_prefill_mma_takes(dtype, a.H, a.G, a.D)) {
-        const size_t sm = (size_t)((a.H * a.H + 3) & ~3) * 4 + (size_t)a.H * MP_BM * MP_RP * 4 + (size_t)2 * 2 * a.G * MP_BN * (a.D + 8) * 2;
-        dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM, a.batch);
-#define TB_MP_LAUNCH(KT) do { allow_smem(attn_mixed_prefill_mma_kernel<KT>, sm); \
-        tb_launch(attn_mixed_prefill_mma_kernel<KT>, grid, dim3(a.H * 32), sm, stream, a); } while (0)
+        MixedAttnArgs am = a;
+        am.stages = mp_smem(a.H, a.G, a.D, 2) <= 200 * 1024 ? 2 : 1;
+        const size_t sm = mp_smem(a.H, a.G, a.D, am.stages);
+        dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM, a.batch, (a.H + 15) / 16);
+        const int warps = a.H < 16 ? a.H : 16;
+#define TB_MP_LAUNCH(KT) do { if (a.H > 16) { allow_smem(attn_mixed_prefill_mma_kernel<KT, true>, sm); \
+            tb_launch(attn_mixed_prefill_mma_kernel<KT, true>, grid, dim3(warps * 32), sm, stream, am); } \
+        else { allow_smem(attn_mixed_prefill_mma_kernel<KT, false>, sm); \
+            tb_launch(attn_mixed_prefill_mma_kernel<KT, false>, grid, dim3(warps * 32), sm, stream, am); } } while (0)
         switch (a.D / 16) { case 2: TB_MP_LAUNCH(2); break; case 4: TB_MP_LAUNCH(4); break; case 6: TB_MP_LAUNCH(6); break; default: TB_MP_LAUNCH(8); break; }
 #undef TB_MP_LAUNCH
         return tb_launch_status();

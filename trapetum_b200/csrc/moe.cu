@@ -28,6 +28,7 @@ struct MoeRouteArgs {
     float weight_eps;
     int softmax;                               // scores are softmax(z) over the experts instead of sigmoid(z)
     float out_scale;                           // the weights times this
+    const float* bias;                         // [E] added to the logits themselves, or null
 };
 
 __device__ __forceinline__ void warp_argmax(float& v, int& i) {
@@ -59,6 +60,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(MoeRouteArgs a) {
             d = (((d + v0) + v1) + v2) + v3;
         }
         for (; sp < a.splits; sp++) d += src[(size_t)sp * a.split_stride];
+        if (a.bias != nullptr && e < a.E) d += a.bias[e];
         const float s = 1.f / (1.f + expf(-d));
         if (e < a.E) { score[e] = a.softmax ? d : s; choice[e] = s + (a.correction ? a.correction[e] : 0.f); }
         else a.gate[t] = s;

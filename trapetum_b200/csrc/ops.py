@@ -1575,14 +1575,14 @@ class _MixedAttnArgs(ctypes.Structure):
                 ("page_rows", c_int), ("ring_rows", c_int), ("len_after", c_void_p), ("out", c_void_p),
                 ("out_stride", c_longlong), ("mix", c_void_p), ("partial", c_void_p), ("H", c_int), ("G", c_int), ("D", c_int),
                 ("n_tokens", c_int), ("window", c_int), ("unit_sink", c_int), ("n_pieces", c_int), ("batch", c_int),
-                ("max_seq_len", c_int)]
+                ("max_seq_len", c_int), ("stages", c_int)]
 
 
 def attn_mixed_padded_head(dtype: torch.dtype, n_heads: int, n: int) -> int:
     """The head size at which a mixer whose scores are mixed across heads stores keys and values of up to ``n`` numbers
-    a head: in bfloat16 with up to 16 heads the next of 32, 64, 96, 128 (what the tensor-core form of its prefill
+    a head: in bfloat16 with up to 32 heads the next of 32, 64, 96, 128 (what the tensor-core form of its prefill
     kernel takes), else the next multiple of 8 (the generic kernels take any size; rows of whole 16-byte pieces)."""
-    if dtype == torch.bfloat16 and n_heads <= 16 and n <= 128:
+    if dtype == torch.bfloat16 and n_heads <= 32 and n <= 128:
         return (n + 31) // 32 * 32
     return (n + 7) // 8 * 8
 
@@ -1653,21 +1653,24 @@ class _MoeRouteArgs(ctypes.Structure):
     _fields_ = [("logits", c_void_p), ("splits", c_int), ("split_stride", c_longlong), ("row_stride", c_longlong),
                 ("correction", c_void_p), ("has_gate", c_int), ("idx", c_void_p), ("weight", c_void_p), ("gate", c_void_p),
                 ("n_tokens", c_int), ("W", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int),
-                ("group_top", c_int), ("weight_eps", c_float), ("softmax", c_int), ("out_scale", c_float)]
+                ("group_top", c_int), ("weight_eps", c_float), ("softmax", c_int), ("out_scale", c_float), ("bias", c_void_p)]
 
 
 def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Tensor], has_gate: bool,
               top: int, groups: int, keep: int, group_top: int, weight_eps: float, score: str = "sigmoid",
-              out_scale: float = 1.0):
+              out_scale: float = 1.0, bias: Optional[torch.Tensor] = None):
     """Routing with groups (see moe.cu; ``score`` "sigmoid" or "softmax" over all experts; the weights come times
     ``out_scale``) from the router's logits: float32 [T, >= experts (+ 1)] or
     partial sums [splits, T, ...] of the router product (column ``experts`` is the shared expert's gate product if
-    ``has_gate``).  Returns (chosen experts int32 [T, top], their weights float32 [T, top], the shared expert's gate
+    ``has_gate``).  ``bias``: float32 [experts] added to the logits themselves (``correction`` only steers the choice).
+    Returns (chosen experts int32 [T, top], their weights float32 [T, top], the shared expert's gate
     float32 [T] or None)."""
-    _cuda(logits, correction)
+    _cuda(logits, correction, bias)
     if logits.dim() == 2:
         logits = logits[None]
     E = experts
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() < E or not bias.is_contiguous()):
+        raise KernelError(f"moe_route: the bias must be contiguous float32 [>= {E}]")
     T = logits.shape[1]
     if logits.dtype != torch.float32 or logits.stride(2) != 1 or logits.shape[2] < E + int(has_gate):
         raise KernelError(f"moe_route: logits must be float32 [splits, T, >= {E + int(has_gate)}], got {tuple(logits.shape)} {logits.dtype}")
@@ -1686,6 +1689,7 @@ def moe_route(logits: torch.Tensor, experts: int, correction: Optional[torch.Ten
     if score not in ("sigmoid", "softmax"):
         raise KernelError(f"moe_route: scores are 'sigmoid' or 'softmax', not '{score}'")
     a.softmax = int(score == "softmax"); a.out_scale = out_scale
+    a.bias = bias.data_ptr() if bias is not None else None
     lib = build.load("moe")
     _check(lib, lib.tb_moe_route(ctypes.byref(a), _stream()), "moe_route")
     return idx, weight, gate

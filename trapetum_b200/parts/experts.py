@@ -11,7 +11,7 @@ of the winners' outputs, plus, if there is a shared expert, ``sigmoid(g . x)`` t
 Two more forms of the same part: ``score`` "softmax" takes ``s = softmax(z)`` over all experts, and ``gated``
 False makes the experts ``down_e(act(up_e x))`` with a unary activation ("relu2", the square of relu) and no gate
 matrix; the shared expert is then of that form too.  ``route_scale`` multiplies the winners' weights.
-``router_bias`` (a tensor name, one number per expert) is added to the logits themselves.  A softmax over the
+``router_bias`` (a tensor name, one number per expert) is added to the logits themselves, by the routing kernel.  A softmax over the
 winners' logits only is ``score`` "softmax" with ``weight_eps`` 0: the winners' shares of the softmax over all
 experts, divided by their sum, are exactly that.
 
@@ -100,9 +100,7 @@ class RoutedExperts(FeedForward):
         self.correction = tensors[self._name("correction")].float().contiguous() if self.params.get("correction") else None
         self.router_bias = None
         if self.params.get("router_bias"):
-            # padded like the router's rows, so that it can be added to the product's first partial sum as it lies
-            b = tensors[self._name("router_bias")].float()
-            self.router_bias = torch.cat([b, torch.zeros(-self.E % 16, dtype=torch.float32, device=b.device)]).contiguous()
+            self.router_bias = tensors[self._name("router_bias")].float().contiguous()      # the routing kernel adds it
         dt = tensors[self._expert(0, "up")].dtype
         self.w_gate = torch.stack([tensors[self._expert(e, "gate")].to(dt) for e in range(self.E)]).contiguous() \
             if self.gated else None
@@ -141,10 +139,9 @@ class RoutedExperts(FeedForward):
         fused_up = self.w_router_up is not None and x.shape[0] <= FUSED_UP_TOKENS
         # 32-bit sums; the routing itself is 32-bit throughout
         logits = linear_partials(x, self.w_router_up if fused_up else self.w_router)
-        if self.router_bias is not None:
-            ops.add_bias(logits[0][:, :self.router_bias.numel()], self.router_bias)
         idx, weight, gate = ops.moe_route(logits, self.E, self.correction, self.has_gate, self.top, self.groups,
-                                          self.keep, self.group_top, self.weight_eps, self.score, self.route_scale)
+                                          self.keep, self.group_top, self.weight_eps, self.score, self.route_scale,
+                                          self.router_bias)
         shared = None
         if self.shared is not None:
             # float32 partial sums [splits, T, hidden]
