@@ -135,6 +135,27 @@ def test_scores_mixed_across_heads_in_prompts(H, G, D, seen, sink, dtype):
         near(got.view(T, H, D), want, dtype, f"mixed attention, prompts ({longest})", rel16=1.5e-2)
 
 
+@pytest.mark.parametrize("H, G, D, seen, sink", [(4, 2, 64, 0, True), (6, 3, 96, -300, True), (2, 1, 128, 500, False), (24, 3, 32, -256, True)])
+def test_scores_mixed_across_heads_in_a_long_prompt_whose_keys_are_cut_into_pieces(H, G, D, seen, sink):
+    """One long prompt is fewer tiles of queries than the GPU has SMs: the tensor-core kernel cuts every tile's keys
+    into pieces and folds them."""
+    from trapetum_b200.csrc import ops
+    dtype = "bfloat16"
+    g = torch.Generator().manual_seed(H + D)
+    lens = [3, 900]
+    T = sum(lens)
+    q = rounded(torch.randn(T, H, D, generator=g), dtype)
+    k = rounded(torch.randn(T, G, D, generator=g), dtype)
+    v = rounded(torch.randn(T, G, D, generator=g), dtype)
+    mix = (torch.eye(H) + 0.4 * torch.randn(H, H, generator=g)).float() * 0.2
+    starts = [0, 3, T]
+    token_seq = [0] * 3 + [1] * 900
+    want = torch.cat([_mixed_reference(q[a:b], k[a:b], v[a:b], mix.double(), H, G, seen, sink) for a, b in zip(starts, starts[1:])])
+    got = ops.attn_mixed_prefill(dev(q.reshape(T, -1), DTYPES[dtype]), dev(k.reshape(T, -1), DTYPES[dtype]),
+                                 dev(v.reshape(T, -1), DTYPES[dtype]), i32(starts), i32(token_seq), H, G, D, dev(mix), seen, sink, 900)
+    near(got.view(T, H, D), want, dtype, "mixed attention, a long prompt in pieces", rel16=1.5e-2)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H, G, D, seen, ring, sink", [(3, 3, 8, -5, 64, True), (6, 3, 24, -33, 0, True), (4, 2, 64, -64, 64, False),
                                                        (2, 1, 40, 0, 0, True), (5, 1, 16, 70, 128, False), (4, 4, 16, -100, 128, True)])

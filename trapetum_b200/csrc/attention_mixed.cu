@@ -355,7 +355,10 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
     pdl_wait();
     const int b = blockIdx.y;
     const int s0 = a.seq_start[b], len = a.seq_start[b + 1] - s0;
-    const int i0 = blockIdx.x * MP_BM;
+    // a tile's keys may be cut into pieces that CTAs of their own take (a short prompt then fills the GPU); their
+    // partial (max, sum, o) are folded by attn_mixed_fold_kernel, in piece order
+    const int P = a.n_pieces > 1 ? a.n_pieces : 1;
+    const int i0 = (blockIdx.x / P) * MP_BM, piece = blockIdx.x % P;
     if (i0 >= len) return;
     const int i_last = min(i0 + MP_BM - 1, len - 1);
     const int ia = i0 + r, ib = i0 + r + 8;                           // the two queries whose scores this thread holds
@@ -393,15 +396,18 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const int j_first = first_seen(a.window, i0);
+    const int j_tile = first_seen(a.window, i0);
+    const int per = (((i_last - j_tile) / MP_BN + 1) + P - 1) / P;    // rounds a piece
+    const int j_first = j_tile + piece * per * MP_BN;
+    const int j_stop = min(i_last, j_first + per * MP_BN - 1);
     const bool two = a.stages >= 2;
-    if (two) load(0, j_first);
+    if (two && j_first <= j_stop) load(0, j_first);
     int st = 0;
-    for (int j0 = j_first; j0 <= i_last; j0 += MP_BN, st ^= (two ? 1 : 0)) {
+    for (int j0 = j_first; j0 <= j_stop; j0 += MP_BN, st ^= (two ? 1 : 0)) {
         if (!two) { __syncthreads(); load(0, j0); }                   // one stage: the round before must have read it
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();                                              // this round's tiles are there; the round before has read its own and the raw scores
-        if (two && j0 + MP_BN <= i_last) load(st ^ 1, j0 + MP_BN);
+        if (two && j0 + MP_BN <= j_stop) load(st ^ 1, j0 + MP_BN);
         const uint32_t t_base = (uint32_t)__cvta_generic_to_shared(tiles + st * stage);
         const uint32_t v_base = t_base + (uint32_t)((k_part + (size_t)(kvh - kv_lo) * MP_BN * PITCH) * 2);
         // ---- raw scores of this head: 16 queries x 32 keys
@@ -495,6 +501,21 @@ __global__ void __launch_bounds__(512) attn_mixed_prefill_mma_kernel(MixedAttnAr
     }
     l_a += __shfl_xor_sync(0xffffffffu, l_a, 1); l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
     l_b += __shfl_xor_sync(0xffffffffu, l_b, 1); l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+    if (P > 1) {
+        if (MULTI && !has_out) return;
+        float* pa_row = a.partial + (((size_t)(s0 + ia) * H + h) * P + piece) * (D + 2);
+        float* pb_row = a.partial + (((size_t)(s0 + ib) * H + h) * P + piece) * (D + 2);
+#pragma unroll
+        for (int n = 0; n < 2 * KT; n++) {
+            if (ia < len) *(float2*)(pa_row + n * 8 + c) = make_float2(o[n][0], o[n][1]);
+            if (ib < len) *(float2*)(pb_row + n * 8 + c) = make_float2(o[n][2], o[n][3]);
+        }
+        if ((lane & 3) == 0) {
+            if (ia < len) { pa_row[D] = m_a; pa_row[D + 1] = l_a; }
+            if (ib < len) { pb_row[D] = m_b; pb_row[D + 1] = l_b; }
+        }
+        return;
+    }
     float inv_a = 1.f / l_a, inv_b = 1.f / l_b;
     if (a.unit_sink) {
         // the denominator also holds exp(0); the sums stand relative to the rows' maxima
@@ -560,7 +581,9 @@ extern "C" int tb_attn_mixed_prefill(const MixedAttnArgs* args, int dtype, cudaS
         MixedAttnArgs am = a;
         am.stages = mp_smem(a.H, a.G, a.D, 2) <= 200 * 1024 ? 2 : 1;
         const size_t sm = mp_smem(a.H, a.G, a.D, am.stages);
-        dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM, a.batch, (a.H + 15) / 16);
+        if (am.n_pieces > 1 && a.partial == nullptr) return tb_refuse("attn_mixed: pieces need scratch");
+        if (am.n_pieces < 1) am.n_pieces = 1;
+        dim3 grid((a.max_seq_len + MP_BM - 1) / MP_BM * am.n_pieces, a.batch, (a.H + 15) / 16);
         const int warps = a.H < 16 ? a.H : 16;
 #define TB_MP_LAUNCH(KT) do { if (a.H > 16) { allow_smem(attn_mixed_prefill_mma_kernel<KT, true>, sm); \
             tb_launch(attn_mixed_prefill_mma_kernel<KT, true>, grid, dim3(warps * 32), sm, stream, am); } \
@@ -568,6 +591,9 @@ extern "C" int tb_attn_mixed_prefill(const MixedAttnArgs* args, int dtype, cudaS
             tb_launch(attn_mixed_prefill_mma_kernel<KT, false>, grid, dim3(warps * 32), sm, stream, am); } } while (0)
         switch (a.D / 16) { case 2: TB_MP_LAUNCH(2); break; case 4: TB_MP_LAUNCH(4); break; case 6: TB_MP_LAUNCH(6); break; default: TB_MP_LAUNCH(8); break; }
 #undef TB_MP_LAUNCH
+        int st = tb_launch_status();
+        if (st || am.n_pieces == 1) return st;
+        TB_DISPATCH_1(dtype, T, tb_launch(attn_mixed_fold_kernel<T>, dim3(a.n_tokens, a.H), dim3(128), 0, stream, am));
         return tb_launch_status();
     }
     const int nc = pick_nc(a.D);

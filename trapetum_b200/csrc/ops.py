@@ -1619,7 +1619,19 @@ def attn_mixed_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, seq_st
     a.seq_start = seq_start.data_ptr(); a.token_seq = token_seq.data_ptr()
     a.batch = seq_start.numel() - 1; a.max_seq_len = int(max_seq_len)
     lib = build.load("attention_mixed")
-    _check(lib, lib.tb_attn_mixed_prefill(ctypes.byref(a), c_int(code(q.dtype)), _stream()), "attn_mixed_prefill")
+    pieces, scratch = 1, None
+    if max_seq_len and lib.tb_attn_mixed_prefill_mma_takes(c_int(code(q.dtype)), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim)):
+        # the tensor-core form takes 16 queries of all heads a CTA: a short step's tiles are fewer than the SMs, so the keys of a
+        # tile are cut into pieces (CTAs of their own, folded afterwards) while that fills the GPU and a piece keeps 4 rounds
+        ctas = (int(max_seq_len) + 15) // 16 * a.batch * ((n_heads + 15) // 16)
+        reach = min(int(max_seq_len), abs(window)) if window else int(max_seq_len)
+        pieces = max(1, min(4, (2 * sm_count(q.device)) // max(1, ctas), reach // 128))
+        if pieces > 1:
+            scratch = torch.empty(q.shape[0] * n_heads * pieces * (head_dim + 2), dtype=torch.float32, device=q.device)
+            a.partial = scratch.data_ptr()
+    a.n_pieces = pieces
+    _check(lib, lib.tb_attn_mixed_prefill(ctypes.byref(a), c_int(code(q.dtype)), _stream()), "attn_mixed_prefill",
+           2 if pieces > 1 else 1)
     return out
 
 
